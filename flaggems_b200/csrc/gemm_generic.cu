@@ -1,0 +1,118 @@
+// Generic GEMM: any dtype (fp32 / fp16 / bf16), any strides, any shape, including
+// K == 0.  Plain fp32 FMA on CUDA cores (fp32 inputs are never rounded to TF32,
+// matching allow_tf32=False in the reference).  This is the correctness path for
+// shapes the tcgen05 kernel does not take; the projection shapes never come here.
+#include "common.cuh"
+
+namespace fg {
+
+int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st);
+bool gemm_tcgen05_eligible(const fg_gemm_params* p);
+
+namespace {
+
+constexpr int TM = 64, TN = 64, TK = 16;
+
+struct GArgs {
+  const void *a, *b, *bias;
+  void* c;
+  int64_t M, N, K;
+  int64_t as0, as1, bs0, bs1, cs0, cs1, zs0, zs1;
+  float alpha, beta;
+  int has_bias;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_generic_kernel(GArgs g) {
+  __shared__ float sa[TK][TM + 4];
+  __shared__ float sb[TK][TN + 4];
+  const T* A = reinterpret_cast<const T*>(g.a);
+  const T* B = reinterpret_cast<const T*>(g.b);
+  const int64_t m0 = (int64_t)blockIdx.y * TM, n0 = (int64_t)blockIdx.x * TN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads, 4x4 outputs each
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int64_t k0 = 0; k0 < g.K; k0 += TK) {
+    // 64x16 elements of A and 16x64 of B: 1024 each, 4 per thread.
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = threadIdx.x + i * 256;
+      {
+        const int kk = e & 15, mm = e >> 4;
+        const int64_t m = m0 + mm, k = k0 + kk;
+        sa[kk][mm] = (m < g.M && k < g.K) ? Cvt<T>::to_f32(A[m * g.as0 + k * g.as1]) : 0.f;
+      }
+      {
+        const int nn = e & 63, kk = e >> 6;
+        const int64_t n = n0 + nn, k = k0 + kk;
+        sb[kk][nn] = (n < g.N && k < g.K) ? Cvt<T>::to_f32(B[k * g.bs0 + n * g.bs1]) : 0.f;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = sa[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = sb[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  T* C = reinterpret_cast<T*>(g.c);
+  const T* Z = reinterpret_cast<const T*>(g.bias);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t m = m0 + ty * 4 + i;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t n = n0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v = acc[i][j];
+      if (g.has_bias) v = v * g.alpha + Cvt<T>::to_f32(Z[m * g.zs0 + n * g.zs1]) * g.beta;
+      C[m * g.cs0 + n * g.cs1] = Cvt<T>::from_f32(v);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace fg
+
+extern "C" int fg_gemm_uses_tcgen05(const fg_gemm_params* p) {
+  return (p != nullptr && fg::gemm_tcgen05_eligible(p)) ? 1 : 0;
+}
+
+extern "C" int fg_gemm(const fg_gemm_params* p, void* stream) {
+  using namespace fg;
+  FG_REQUIRE(p != nullptr, "gemm: null params");
+  FG_REQUIRE(p->M >= 0 && p->N >= 0 && p->K >= 0, "gemm: negative size");
+  if (p->M == 0 || p->N == 0) return FG_OK;
+  FG_REQUIRE(p->c != nullptr, "gemm: null output");
+  FG_REQUIRE(p->K == 0 || (p->a && p->b), "gemm: null operand");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (gemm_tcgen05_eligible(p)) return gemm_tcgen05(p, st);
+
+  GArgs g;
+  g.a = p->a; g.b = p->b; g.bias = p->bias; g.c = p->c;
+  g.M = p->M; g.N = p->N; g.K = p->K;
+  g.as0 = p->a_stride0; g.as1 = p->a_stride1; g.bs0 = p->b_stride0; g.bs1 = p->b_stride1;
+  g.cs0 = p->c_stride0; g.cs1 = p->c_stride1; g.zs0 = p->bias_stride0; g.zs1 = p->bias_stride1;
+  g.alpha = (float)p->alpha; g.beta = (float)p->beta;
+  g.has_bias = p->bias != nullptr;
+  const int64_t gx = (p->N + TN - 1) / TN, gy = (p->M + TM - 1) / TM;
+  if (gy > 65535) return fail(FG_ERR_TOO_LARGE, "gemm (generic path): M = %lld exceeds %d rows", (long long)p->M,
+                              65535 * TM);
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  FG_DISPATCH_FLOAT(p->dtype, T, gemm_generic_kernel<T><<<grid, 256, 0, st>>>(g));
+  FG_CHECK_LAUNCH("gemm_generic_kernel");
+  return FG_OK;
+}

@@ -1,0 +1,373 @@
+// Dense GEMM for the mm/addmm projections on sm_100a:
+//   C[M,N] = alpha * A[M,K] @ B[K,N] (+ beta * bias), 16-bit inputs, fp32 accumulate.
+//
+// Persistent kernel, one CTA per SM, 128x256 output tile, BK = 64:
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A and B into a 4-stage
+//               128-byte-swizzled shared-memory ring (48 KB per stage)
+//   warp 1      allocates TMEM and issues tcgen05.mma (M128 N256 K16) from one thread;
+//               two 256-column fp32 accumulators so tile i+1 overlaps the epilogue of i
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, alpha/beta/bias in fp32, round
+//               once, 16-byte stores
+// Both operands may be row- or column-major; the UMMA descriptors carry the
+// majorness, the TMA boxes differ (one [64 x rows] box for a K-major operand, one
+// [64 x 64] box per 64 rows for an MN-major operand).  M, N and K tails are handled
+// by TMA zero fill on loads and predication on stores.
+#include "common.cuh"
+#include "sm100_common.cuh"
+
+namespace fg {
+
+int* device_status_ptr();
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+
+struct GemmArgs {
+  void* c;
+  const void* bias;
+  int64_t M, N, K;
+  int64_t c_s0;                // C row stride (unit column stride)
+  int64_t bias_s0, bias_s1;
+  float alpha, beta;
+  int has_bias;
+  int a_mn_major, b_mn_major;  // 0: K contiguous, 1: M / N contiguous
+  int is_bf16;
+  int group_m;
+  int c_vec_ok;                // 16-byte stores legal for C
+  int* status;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 v = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int group_m,
+                                            int64_t& tm, int64_t& tn) {
+  // Grouped ordering: `group_m` row tiles share each sweep over the column tiles so
+  // the A panels of a group and the B panels in flight stay L2 resident.
+  const int64_t per_group = (int64_t)group_m * tiles_n;
+  const int64_t g = tile / per_group;
+  const int64_t first_m = g * group_m;
+  const int64_t rows = (tiles_m - first_m) < group_m ? (tiles_m - first_m) : group_m;
+  const int64_t r = tile - g * per_group;
+  tm = first_m + r % rows;
+  tn = r / rows;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    GemmArgs g) {
+  using namespace sm100;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bars_base = smem + STAGES * STAGE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(bars_base);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int64_t tiles_m = (g.M + BM - 1) / BM;
+  const int64_t tiles_n = (g.N + BN - 1) / BN;
+  const int64_t num_tiles = tiles_m * tiles_n;
+  const int num_kb = (int)((g.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int64_t tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, g.group_m, tm, tn);
+        const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, kStatusGemmTimeout)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!g.a_mn_major) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BM / 64; ++b)
+              tma_load_2d(sa + b * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + 64 * b, k0);
+          }
+          if (!g.b_mn_major) {
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BN / 64; ++b)
+              tma_load_2d(sb + b * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + 64 * b, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(g.is_bf16 != 0, g.a_mn_major != 0, g.b_mn_major != 0, BM, BN);
+      // Per-operand descriptor geometry.
+      const uint32_t a_lbo = g.a_mn_major ? 64 * BK * 2 : 0, b_lbo = g.b_mn_major ? 64 * BK * 2 : 0;
+      const uint32_t a_kstep = g.a_mn_major ? 16 * 128 : 32;  // bytes per K=16 step
+      const uint32_t b_kstep = g.b_mn_major ? 16 * 128 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int64_t local = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = (int)(local & 1);
+        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, g.status, kStatusGemmTimeout)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag, g.status, kStatusGemmTimeout)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = umma_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
+            const uint64_t bdesc = umma_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
+            mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    int64_t local = 0;
+    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int buf = (int)(local & 1);
+      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, g.group_m, tm, tn);
+      if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, g.status, kStatusGemmTimeout)) break;
+      tc_fence_after();
+      const int64_t row = tm * BM + quarter * 32 + lane;
+      const int64_t col0 = tn * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      T* crow = reinterpret_cast<T*>(g.c) + row * g.c_s0;
+      const T* bias = reinterpret_cast<const T*>(g.bias);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        const int64_t col = col0 + c * 32;
+        if (row < g.M && col < g.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          if (g.has_bias) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int64_t cj = col + j;
+              const float bv = cj < g.N ? Cvt<T>::to_f32(bias[row * g.bias_s0 + cj * g.bias_s1]) : 0.f;
+              v[j] = v[j] * g.alpha + bv * g.beta;
+            }
+          }
+          if (g.c_vec_ok && col + 32 <= g.N) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 o;
+              o.x = pack2<T>(v[q * 8 + 0], v[q * 8 + 1]);
+              o.y = pack2<T>(v[q * 8 + 2], v[q * 8 + 3]);
+              o.z = pack2<T>(v[q * 8 + 4], v[q * 8 + 5]);
+              o.w = pack2<T>(v[q * 8 + 6], v[q * 8 + 7]);
+              *reinterpret_cast<uint4*>(crow + col + q * 8) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col + j < g.N) crow[col + j] = Cvt<T>::from_f32(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ------------------------------ teardown -------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // Give copies and MMAs still in flight a bounded time to land before the
+      // accumulator columns are handed back.
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace
+
+static bool tcgen05_eligible(const fg_gemm_params* p) {
+  if (p->dtype != FG_BF16 && p->dtype != FG_F16) return false;
+  if (p->M < 1 || p->N < 1 || p->K < 1) return false;
+  if (p->M > 2147483647LL || p->N > 2147483647LL || p->K > 2147483647LL) return false;
+  // Tiny problems are launch-bound; the generic kernel handles them without a
+  // tensor map.  (Also keeps odd test shapes off the TMA alignment rules.)
+  if (p->M * p->N < 64 * 64 || p->K < 32) return false;
+  auto operand_ok = [](const void* ptr, int64_t s0, int64_t s1, int64_t rows, int64_t cols) {
+    // either unit stride along dim1 (row-major) or along dim0 (column-major); the
+    // other stride a multiple of 8 elements (16 B); base 16-byte aligned
+    if (!aligned16(ptr)) return false;
+    if (s1 == 1 && (s0 % 8 == 0) && s0 >= cols) return true;
+    if (s0 == 1 && (s1 % 8 == 0) && s1 >= rows) return true;
+    return false;
+  };
+  if (!operand_ok(p->a, p->a_stride0, p->a_stride1, p->M, p->K)) return false;
+  if (!operand_ok(p->b, p->b_stride0, p->b_stride1, p->K, p->N)) return false;
+  if (p->c_stride1 != 1) return false;
+  return true;
+}
+
+int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
+  using namespace fg;
+  // A: K-major if a_stride1 == 1 (row-major), else M-major.  Degenerate shapes with
+  // both strides 1 are treated as row-major.
+  const bool a_mn = !(p->a_stride1 == 1 && p->a_stride0 % 8 == 0 && p->a_stride0 >= p->K);
+  // B [K,N]: K-major if b_stride0 == 1 (column-major storage), else N-major.
+  const bool b_mn = !(p->b_stride0 == 1 && p->b_stride1 % 8 == 0 && p->b_stride1 >= p->K);
+
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2], strides[1];
+    uint32_t box[2];
+    if (!a_mn) {
+      dims[0] = (uint64_t)p->K; dims[1] = (uint64_t)p->M; strides[0] = (uint64_t)p->a_stride0 * 2;
+      box[0] = 64; box[1] = BM;
+    } else {
+      dims[0] = (uint64_t)p->M; dims[1] = (uint64_t)p->K; strides[0] = (uint64_t)p->a_stride1 * 2;
+      box[0] = 64; box[1] = BK;
+    }
+    int rc = encode_tmap_16bit(&ta, p->a, 2, dims, strides, box);
+    if (rc != FG_OK) return rc;
+    if (!b_mn) {
+      dims[0] = (uint64_t)p->K; dims[1] = (uint64_t)p->N; strides[0] = (uint64_t)p->b_stride1 * 2;
+      box[0] = 64; box[1] = BN;
+    } else {
+      dims[0] = (uint64_t)p->N; dims[1] = (uint64_t)p->K; strides[0] = (uint64_t)p->b_stride0 * 2;
+      box[0] = 64; box[1] = BK;
+    }
+    rc = encode_tmap_16bit(&tb, p->b, 2, dims, strides, box);
+    if (rc != FG_OK) return rc;
+  }
+  GemmArgs g;
+  g.c = p->c; g.bias = p->bias;
+  g.M = p->M; g.N = p->N; g.K = p->K;
+  g.c_s0 = p->c_stride0;
+  g.bias_s0 = p->bias_stride0; g.bias_s1 = p->bias_stride1;
+  g.alpha = (float)p->alpha; g.beta = (float)p->beta;
+  g.has_bias = p->bias != nullptr;
+  g.a_mn_major = a_mn; g.b_mn_major = b_mn;
+  g.is_bf16 = p->dtype == FG_BF16;
+  g.group_m = 8;
+  g.c_vec_ok = aligned16(p->c) && (p->c_stride0 % 8 == 0);
+  g.status = device_status_ptr();
+  if (!g.status) return fail(FG_ERR_CUDA, "gemm: device status word unavailable");
+
+  const int64_t tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN);
+  int grid = num_sms();
+  if (tiles < grid) grid = (int)tiles;
+  if (p->dtype == FG_BF16) {
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_dev = dev;
+    }
+    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, g);
+  } else {
+    static thread_local int attr_dev = -1;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (attr_dev != dev) {
+      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_dev = dev;
+    }
+    gemm_tcgen05_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, g);
+  }
+  FG_CHECK_LAUNCH("gemm_tcgen05_kernel");
+  return FG_OK;
+}
+
+bool gemm_tcgen05_eligible(const fg_gemm_params* p) { return tcgen05_eligible(p); }
+
+}  // namespace fg

@@ -1,0 +1,119 @@
+// reshape_and_cache_flash: scatter new K/V rows into a paged cache (pure copy,
+// bit-exact).  Work is flattened over (token, K|V, 16-byte packet) so that small
+// decode batches still spread over many CTAs and large prefill batches stream at
+// HBM rate; the scalar kernel handles unaligned layouts element by element.
+#include "common.cuh"
+
+namespace fg {
+
+struct CacheArgs {
+  const char *key, *value;
+  char *kc, *vc;
+  const int64_t* slots;
+  int64_t T;
+  int64_t H, D, BS, NB;
+  int64_t ks, vs;          // token strides of key / value (elements)
+  int64_t cbs, crs, chs;   // cache block / row / head strides (elements)
+};
+
+// One packet = 16 bytes inside one head row (D*ES is a multiple of 16).
+template <int ES>
+__global__ void __launch_bounds__(256) cache_scatter_vec_kernel(CacheArgs a, int packs_per_head) {
+  const int64_t packs_per_tok = a.H * packs_per_head;
+  const int64_t total = a.T * packs_per_tok * 2;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tk = idx / packs_per_tok;  // token * 2 + which
+    const int64_t r = idx - tk * packs_per_tok;
+    const int64_t tok = tk >> 1;
+    const int which = (int)(tk & 1);
+    const int64_t slot = a.slots[tok];
+    if (slot < 0 || slot >= a.NB * a.BS) continue;  // padding, or outside the cache
+    const int64_t h = r / packs_per_head;
+    const int64_t c = r - h * packs_per_head;
+    const int64_t blk = slot / a.BS, off = slot - blk * a.BS;
+    const char* src = (which ? a.value + tok * a.vs * ES : a.key + tok * a.ks * ES) +
+                      (h * a.D) * ES + c * 16;
+    char* dst = (which ? a.vc : a.kc) + (blk * a.cbs + off * a.crs + h * a.chs) * ES + c * 16;
+    uint4 v;
+    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(src));
+    *reinterpret_cast<uint4*>(dst) = v;
+  }
+}
+
+template <typename U>
+__global__ void __launch_bounds__(256) cache_scatter_scalar_kernel(CacheArgs a) {
+  const int64_t n = a.H * a.D;
+  const int64_t total = a.T * n * 2;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tk = idx / n;
+    const int64_t i = idx - tk * n;
+    const int64_t tok = tk >> 1;
+    const int which = (int)(tk & 1);
+    const int64_t slot = a.slots[tok];
+    if (slot < 0 || slot >= a.NB * a.BS) continue;  // padding, or outside the cache
+    const int64_t h = i / a.D, d = i - h * a.D;
+    const int64_t blk = slot / a.BS, off = slot - blk * a.BS;
+    const U* src = reinterpret_cast<const U*>(which ? a.value : a.key) + tok * (which ? a.vs : a.ks) + i;
+    U* dst = reinterpret_cast<U*>(which ? a.vc : a.kc) + blk * a.cbs + off * a.crs + h * a.chs + d;
+    *dst = *src;
+  }
+}
+
+}  // namespace fg
+
+extern "C" int fg_reshape_and_cache_flash(const void* key, const void* value, void* key_cache,
+                                          void* value_cache, const int64_t* slot_mapping,
+                                          int64_t num_tokens, int64_t num_heads, int64_t head_size,
+                                          int64_t block_size, int64_t num_blocks,
+                                          int64_t key_stride, int64_t value_stride, int64_t cache_block_stride,
+                                          int64_t cache_row_stride, int64_t cache_head_stride,
+                                          int elem_size, void* stream) {
+  using namespace fg;
+  FG_REQUIRE(num_tokens >= 0 && num_heads >= 0 && head_size >= 0, "reshape_and_cache_flash: negative size");
+  FG_REQUIRE(block_size > 0 && num_blocks >= 0, "reshape_and_cache_flash: block_size must be positive");
+  FG_REQUIRE(elem_size == 1 || elem_size == 2 || elem_size == 4,
+             "reshape_and_cache_flash: element size %d not in {1,2,4}", elem_size);
+  if (num_tokens == 0 || num_heads * head_size == 0) return FG_OK;
+  FG_REQUIRE(key && value && key_cache && value_cache && slot_mapping,
+             "reshape_and_cache_flash: null pointer");
+  CacheArgs a;
+  a.key = (const char*)key; a.value = (const char*)value;
+  a.kc = (char*)key_cache; a.vc = (char*)value_cache;
+  a.slots = slot_mapping; a.T = num_tokens; a.H = num_heads; a.D = head_size; a.BS = block_size; a.NB = num_blocks;
+  a.ks = key_stride; a.vs = value_stride;
+  a.cbs = cache_block_stride; a.crs = cache_row_stride; a.chs = cache_head_stride;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int es = elem_size;
+  auto b16 = [&](int64_t elems) { return (elems * es) % 16 == 0; };
+  const bool vec = b16(head_size) && b16(key_stride) && b16(value_stride) && b16(cache_block_stride) &&
+                   b16(cache_row_stride) && b16(cache_head_stride) && aligned16(key) &&
+                   aligned16(value) && aligned16(key_cache) && aligned16(value_cache);
+  const int64_t cap = (int64_t)num_sms() * 16;
+  if (vec) {
+    const int pph = (int)(head_size * es / 16);
+    const int64_t total = num_tokens * num_heads * pph * 2;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    switch (es) {
+      case 1: cache_scatter_vec_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(a, pph); break;
+      case 2: cache_scatter_vec_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(a, pph); break;
+      default: cache_scatter_vec_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(a, pph); break;
+    }
+    FG_CHECK_LAUNCH("cache_scatter_vec_kernel");
+  } else {
+    const int64_t total = num_tokens * num_heads * head_size * 2;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > cap) blocks = cap;
+    switch (es) {
+      case 1: cache_scatter_scalar_kernel<uint8_t><<<(unsigned)blocks, 256, 0, st>>>(a); break;
+      case 2: cache_scatter_scalar_kernel<uint16_t><<<(unsigned)blocks, 256, 0, st>>>(a); break;
+      default: cache_scatter_scalar_kernel<uint32_t><<<(unsigned)blocks, 256, 0, st>>>(a); break;
+    }
+    FG_CHECK_LAUNCH("cache_scatter_scalar_kernel");
+  }
+  return FG_OK;
+}

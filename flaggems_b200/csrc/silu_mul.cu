@@ -1,0 +1,152 @@
+// silu_and_mul: out = silu(fp32(a)) * b  (HBM-bound elementwise).
+// Fast kernel: tensors viewed as [rows, cols] with unit column stride, 16-byte
+// packets, two packets of each operand in flight per thread.  Generic kernel:
+// up to 6 broadcast dimensions with arbitrary element strides.
+#include "common.cuh"
+
+namespace fg {
+
+__device__ __forceinline__ float silu_mul_f32(float x, float y) {
+  return x / (1.0f + __expf(-x)) * y;
+}
+
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(256)
+silu_mul_rows_kernel(const T* a, const T* b, T* out,
+                     int64_t total_packs, int packs_per_row, int64_t a_stride, int64_t b_stride,
+                     int64_t o_stride) {
+  constexpr int E = Pack16<T>::N;
+  const int64_t base = ((int64_t)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
+  Pack16<T> pa[UNROLL], pb[UNROLL];
+  int64_t ooff[UNROLL];
+  bool ok[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    const int64_t idx = base + (int64_t)u * blockDim.x;
+    ok[u] = idx < total_packs;
+    if (ok[u]) {
+      const int64_t row = idx / packs_per_row;
+      const int64_t col = (idx - row * packs_per_row) * E;
+      pa[u] = ld16_stream(a + row * a_stride + col);
+      pb[u] = ld16_stream(b + row * b_stride + col);
+      ooff[u] = row * o_stride + col;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    if (ok[u]) {
+      Pack16<T> o;
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        o.v[e] = Cvt<T>::from_f32(silu_mul_f32(Cvt<T>::to_f32(pa[u].v[e]), Cvt<T>::to_f32(pb[u].v[e])));
+      st16(out + ooff[u], o);
+    }
+  }
+}
+
+struct Strided6 {
+  int64_t size[6];
+  int64_t sa[6], sb[6], so[6];
+  int ndim;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+silu_mul_strided_kernel(const T* a, const T* b, T* out,
+                        int64_t total, Strided6 d) {
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    int64_t rem = idx, oa = 0, ob = 0, oo = 0;
+#pragma unroll
+    for (int k = 5; k >= 0; --k) {
+      if (k < d.ndim) {
+        const int64_t q = rem / d.size[k];
+        const int64_t r = rem - q * d.size[k];
+        rem = q;
+        oa += r * d.sa[k];
+        ob += r * d.sb[k];
+        oo += r * d.so[k];
+      }
+    }
+    out[oo] = Cvt<T>::from_f32(silu_mul_f32(Cvt<T>::to_f32(a[oa]), Cvt<T>::to_f32(b[ob])));
+  }
+}
+
+template <typename T>
+static int launch_silu_mul(const T* a, const T* b, T* out, int ndim, const int64_t* sizes,
+                           const int64_t* sa, const int64_t* sb, const int64_t* so,
+                           cudaStream_t st) {
+  constexpr int E = Pack16<T>::N;
+  int64_t total = 1;
+  for (int i = 0; i < ndim; ++i) total *= sizes[i];
+  if (total == 0) return FG_OK;
+
+  // Try to view the problem as [rows, cols]: the last dim has unit stride in all
+  // three tensors and every leading dim folds into one uniform row stride.
+  bool rows_ok = ndim >= 1 && sa[ndim - 1] == 1 && sb[ndim - 1] == 1 && so[ndim - 1] == 1;
+  int64_t cols = ndim >= 1 ? sizes[ndim - 1] : 1, rows = 1;
+  int64_t ras = 0, rbs = 0, ros = 0;
+  if (rows_ok) {
+    // fold dims ndim-2 .. 0: need stride[k] == stride[k+1]*size[k+1] for k < ndim-2
+    bool first = true;
+    for (int k = ndim - 2; k >= 0 && rows_ok; --k) {
+      if (sizes[k] == 1) continue;
+      if (first) {
+        ras = sa[k]; rbs = sb[k]; ros = so[k];
+        rows = sizes[k];
+        first = false;
+      } else {
+        rows_ok = sa[k] == ras * rows && sb[k] == rbs * rows && so[k] == ros * rows;
+        rows *= sizes[k];
+      }
+    }
+    rows_ok = rows_ok && (cols % E == 0) && aligned16(a) && aligned16(b) && aligned16(out) &&
+              (ras % E == 0) && (rbs % E == 0) && (ros % E == 0);
+  }
+  if (rows_ok && cols / E <= 2147483647LL) {
+    constexpr int UNROLL = 2;
+    const int64_t total_packs = total / E;
+    const int64_t blocks = (total_packs + 256 * UNROLL - 1) / (256 * UNROLL);
+    if (blocks > 2147483647LL) return fail(FG_ERR_TOO_LARGE, "silu_and_mul: tensor too large");
+    silu_mul_rows_kernel<T, UNROLL><<<(unsigned)blocks, 256, 0, st>>>(
+        a, b, out, total_packs, (int)(cols / E), ras, rbs, ros);
+    FG_CHECK_LAUNCH("silu_mul_rows_kernel");
+    return FG_OK;
+  }
+  Strided6 d;
+  d.ndim = ndim;
+  for (int i = 0; i < 6; ++i) {
+    d.size[i] = i < ndim ? sizes[i] : 1;
+    d.sa[i] = i < ndim ? sa[i] : 0;
+    d.sb[i] = i < ndim ? sb[i] : 0;
+    d.so[i] = i < ndim ? so[i] : 0;
+  }
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)num_sms() * 32;
+  if (blocks > cap) blocks = cap;
+  silu_mul_strided_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, total, d);
+  FG_CHECK_LAUNCH("silu_mul_strided_kernel");
+  return FG_OK;
+}
+
+}  // namespace fg
+
+extern "C" int fg_silu_and_mul(const void* a, const void* b, void* out, int ndim,
+                               const int64_t* sizes, const int64_t* a_strides,
+                               const int64_t* b_strides, const int64_t* o_strides, int dtype,
+                               void* stream) {
+  using namespace fg;
+  FG_REQUIRE(ndim >= 0 && ndim <= 6, "silu_and_mul: ndim %d not in [0, 6]", ndim);
+  FG_REQUIRE(ndim == 0 || (sizes && a_strides && b_strides && o_strides),
+             "silu_and_mul: null shape/stride array");
+  for (int i = 0; i < ndim; ++i) {
+    FG_REQUIRE(sizes[i] >= 0, "silu_and_mul: negative size");
+    if (sizes[i] == 0) return FG_OK;
+  }
+  FG_REQUIRE(a && b && out, "silu_and_mul: null pointer");
+  FG_DISPATCH_FLOAT(dtype, T,
+                    return (launch_silu_mul<T>((const T*)a, (const T*)b, (T*)out, ndim, sizes,
+                                               a_strides, b_strides, o_strides,
+                                               (cudaStream_t)stream)));
+  return FG_OK;
+}

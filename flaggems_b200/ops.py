@@ -1,0 +1,337 @@
+"""Tensor-core operators of the inference path: the mm/addmm projections,
+``flash_attn_varlen_func`` and plain ``rms_norm``.
+
+Same names, argument meaning and error behaviour as ``flag_gems.ops``
+(``src/flag_gems/ops/mm.py``, ``addmm.py``, ``attention.py``, ``flash_api.py``,
+``rms_norm.py``).  Host code validates and allocates outputs with torch; all
+arithmetic runs in the sm_100a kernels behind the C ABI.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import logging
+import math
+
+import torch
+
+from . import _lib
+
+logger = logging.getLogger("flag_gems." + __name__.split(".")[-1])
+
+__all__ = ["mm", "mm_out", "addmm", "addmm_out", "flash_attn_varlen_func", "rms_norm", "get_higher_dtype"]
+
+_ordered_datatypes = [torch.float16, torch.bfloat16, torch.float32]
+
+
+def get_higher_dtype(a, b):
+    """Output dtype rule of the reference mm (src/flag_gems/ops/mm.py:140-151)."""
+    if a is b:
+        return a
+    assert a in _ordered_datatypes
+    assert b in _ordered_datatypes
+    for d in _ordered_datatypes:
+        if a is d:
+            return b
+        if b is d:
+            return a
+
+
+def broadcastable_to(s1, s2) -> bool:
+    r1, r2 = len(s1), len(s2)
+    if r1 == 0:
+        return True
+    if r2 == 0:
+        return False
+    if r1 > r2:
+        return False
+    for i in range(1, r1 + 1):
+        if s1[-i] != 1 and s1[-i] != s2[-i]:
+            return False
+    return True
+
+
+def _gemm(a, b, c, bias=None, alpha=1.0, beta=1.0):
+    dev = _lib.require_cuda(a, b, c, bias)
+    p = _lib.GemmParams()
+    p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    p.bias = None if bias is None else bias.data_ptr()
+    p.M, p.K = a.shape
+    p.N = b.shape[1]
+    p.a_stride0, p.a_stride1 = a.stride()
+    p.b_stride0, p.b_stride1 = b.stride()
+    p.c_stride0, p.c_stride1 = c.stride()
+    if bias is not None:
+        p.bias_stride0, p.bias_stride1 = bias.stride()
+    p.alpha, p.beta = float(alpha), float(beta)
+    p.dtype = _lib.dtype_code(c.dtype)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().fg_gemm(C.byref(p), _lib.stream_ptr(dev)))
+    return c
+
+
+def _prep_mm(a, b):
+    _lib.require_cuda(a, b)
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("mm: both arguments must be 2-D")
+    assert a.shape[1] == b.shape[0], "incompatible dimensions"
+    # same normalisation as the reference: only a tensor strided in BOTH dims is copied
+    if a.stride(0) > 1 and a.stride(1) > 1:
+        a = a.contiguous()
+    if b.stride(0) > 1 and b.stride(1) > 1:
+        b = b.contiguous()
+    c_dtype = get_higher_dtype(a.dtype, b.dtype)
+    if a.dtype != c_dtype:
+        a = a.to(c_dtype)
+    if b.dtype != c_dtype:
+        b = b.to(c_dtype)
+    return a, b, c_dtype
+
+
+def mm(a, b):
+    """``a @ b`` with fp32 accumulation (aten::mm override)."""
+    a, b, c_dtype = _prep_mm(a, b)
+    M, K = a.shape
+    N = b.shape[1]
+    logger.debug("GEMS MM, [shape info]: [-, %s, %s, %s](batch, M, N, K), [A column-major]: %s, "
+                 "[B column-major]: %s", M, N, K, a.stride(0) == 1, b.stride(0) == 1)
+    c = torch.empty((M, N), device=a.device, dtype=c_dtype)
+    return _gemm(a, b, c)
+
+
+def mm_out(a, b, *, out):
+    """``out = a @ b`` (aten::mm.out override)."""
+    a, b, c_dtype = _prep_mm(a, b)
+    M, K = a.shape
+    N = b.shape[1]
+    if tuple(out.shape) != (M, N):
+        raise RuntimeError(f"mm_out: out has shape {tuple(out.shape)}, expected {(M, N)}")
+    if out.dtype != c_dtype:
+        raise RuntimeError(f"mm_out: out has dtype {out.dtype}, expected {c_dtype}")
+    logger.debug("GEMS MM_OUT, [shape info]: [-, %s, %s, %s](batch, M, N, K)", M, N, K)
+    return _gemm(a, b, out)
+
+
+def _prep_addmm(bias, mat1, mat2):
+    _lib.require_cuda(bias, mat1, mat2)
+    assert mat1.shape[1] == mat2.shape[0], "Incompatible dimensions"
+    assert broadcastable_to(bias.shape, (mat1.shape[0], mat2.shape[1])), "Incompatible input shape"
+    if mat1.dtype != mat2.dtype or bias.dtype != mat1.dtype:
+        raise RuntimeError("addmm: bias, mat1 and mat2 must share a dtype")
+    mat1 = mat1.contiguous()
+    if mat2.stride(0) > 1 and mat2.stride(1) > 1:
+        mat2 = mat2.contiguous()
+    return mat1, mat2
+
+
+def addmm(bias, mat1, mat2, *, beta=1, alpha=1):
+    """``beta * bias + alpha * (mat1 @ mat2)``, epilogue in fp32 (aten::addmm override)."""
+    mat1, mat2 = _prep_addmm(bias, mat1, mat2)
+    M, K = mat1.shape
+    N = mat2.shape[1]
+    logger.debug("GEMS ADDMM, [shape info]: [-, %s, %s, %s](batch, M, N, K), [A column-major]: %s, "
+                 "[B column-major]: %s, [bias column-major]: %s", M, N, K, mat1.stride(0) == 1,
+                 mat2.stride(0) == 1, bias.dim() > 0 and bias.stride(0) == 1)
+    out = torch.empty((M, N), device=mat1.device, dtype=mat1.dtype)
+    return _gemm(mat1, mat2, out, bias.broadcast_to(out.shape), alpha, beta)
+
+
+def addmm_out(bias, mat1, mat2, *, beta=1, alpha=1, out=None):
+    """``out = beta * bias + alpha * (mat1 @ mat2)`` (aten::addmm.out override)."""
+    mat1, mat2 = _prep_addmm(bias, mat1, mat2)
+    M, K = mat1.shape
+    N = mat2.shape[1]
+    if out is None:
+        out = torch.empty((M, N), device=mat1.device, dtype=mat1.dtype)
+    else:
+        assert out.shape == (M, N), "Incompatible output shape"
+        if out.dtype != mat1.dtype:
+            raise RuntimeError("addmm_out: out must have the dtype of mat1")
+    logger.debug("GEMS ADDMM_OUT, [shape info]: [-, %s, %s, %s](batch, M, N, K)", M, N, K)
+    return _gemm(mat1, mat2, out, bias.broadcast_to(out.shape), alpha, beta)
+
+
+# ---------------------------------------------------------------------------
+# rms_norm (src/flag_gems/ops/rms_norm.py:221; inference forward only)
+# ---------------------------------------------------------------------------
+def rms_norm(x, normalized_shape, weight, eps=1e-5):
+    """``x * rsqrt(mean(x^2) + eps) * weight`` over the trailing ``normalized_shape``."""
+    logger.debug("GEMS RMS_NORM FORWARD")
+    dev = _lib.require_cuda(x, weight)
+    N = math.prod(normalized_shape)
+    if tuple(x.shape[x.ndim - len(normalized_shape):]) != tuple(normalized_shape):
+        raise RuntimeError("rms_norm: normalized_shape does not match the trailing dims of input")
+    if weight.numel() != N or weight.dtype != x.dtype:
+        raise RuntimeError("rms_norm: weight must match normalized_shape and the input dtype")
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    M = xc.numel() // N if N else 0
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().fg_rms_norm(
+            xc.data_ptr(), weight.contiguous().data_ptr(), out.data_ptr(), M, N, N, N, float(eps),
+            _lib.dtype_code(x.dtype), _lib.stream_ptr(dev)))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# flash_attn_varlen_func (src/flag_gems/ops/attention.py:1118-1287,
+#                         src/flag_gems/ops/flash_api.py:230-569)
+# ---------------------------------------------------------------------------
+def maybe_contiguous(x):
+    return x.contiguous() if x is not None and x.stride(-1) != 1 else x
+
+
+_workspaces: dict = {}
+
+
+def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) scratch for split-KV decode; grows monotonically so that
+    steady-state decode steps allocate nothing."""
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _workspaces[key] = ws
+    return ws
+
+
+def flash_attn_varlen_func(
+    q,
+    k,
+    v,
+    max_seqlen_q,
+    cu_seqlens_q,
+    max_seqlen_k,
+    cu_seqlens_k=None,  # only used for non-paged prefill
+    seqused_k=None,
+    q_v=None,
+    dropout_p=0.0,
+    softmax_scale=None,
+    causal=False,
+    window_size=None,
+    softcap=0.0,  # 0.0 means deactivated
+    alibi_slopes=None,
+    deterministic=False,
+    return_attn_probs=False,
+    block_table=None,
+    return_softmax_lse=False,
+    out=None,
+    # Dummy FA3 arguments
+    scheduler_metadata=None,
+    q_descale=None,
+    k_descale=None,
+    v_descale=None,
+    num_splits: int = 0,
+    fa_version: int = 2,
+):
+    """FlashAttention-2 forward over variable-length sequences (vLLM-compatible signature).
+
+    q: ``(total_q, nheads, headdim)``.  Paged form (``block_table`` given): k, v are
+    ``(num_blocks, block_size, nheads_k, headdim)`` and ``seqused_k`` holds the key
+    lengths.  Contiguous form: k, v are ``(total_k, nheads_k, headdim)`` indexed by
+    ``cu_seqlens_k`` (the reference accepts the paged form only, flash_api.py:272).
+    The causal mask is aligned to the bottom-right corner; rows that see no key
+    produce zeros.  Returns ``out`` or ``(out, softmax_lse)`` with lse ``(nheads, total_q)``.
+    """
+    logger.debug("GEMS FLASH_ATTN_VARLEN_FUNC")
+    assert cu_seqlens_k is not None or seqused_k is not None, "cu_seqlens_k or seqused_k must be provided"
+    assert cu_seqlens_k is None or seqused_k is None, (
+        "cu_seqlens_k and seqused_k cannot be provided at the same time")
+    assert block_table is None or seqused_k is not None, "seqused_k must be provided if block_table is provided"
+    if block_table is None and cu_seqlens_k is None:
+        raise RuntimeError("flash_attn_varlen_func: the contiguous KV form needs cu_seqlens_k")
+    if softmax_scale is None:
+        softmax_scale = q.shape[-1] ** (-0.5)
+    if window_size is None:
+        real_window_size = (-1, -1)
+    else:
+        assert len(window_size) == 2
+        real_window_size = (int(window_size[0]), int(window_size[1]))
+    if fa_version != 2:
+        raise RuntimeError("Only FA2 is implemented.")
+    if num_splits > 0:
+        raise RuntimeError("num_splits > 0 is not implemented in GEMS.")
+    if dropout_p != 0.0:
+        raise RuntimeError("flash_attn_varlen_func: dropout is not supported on the inference path")
+    if q_v is not None:
+        raise RuntimeError("flash_attn_varlen_func: q_v is not supported")
+    if return_attn_probs:
+        raise RuntimeError("flash_attn_varlen_func: return_attn_probs needs dropout, which is not supported")
+    dev = _lib.require_cuda(q, k, v, cu_seqlens_q, cu_seqlens_k, seqused_k, block_table, alibi_slopes, out)
+    q, k, v = [maybe_contiguous(x) for x in (q, k, v)]
+    max_seqlen_q = max_seqlen_q.item() if hasattr(max_seqlen_q, "item") else max_seqlen_q
+    max_seqlen_k = max_seqlen_k.item() if hasattr(max_seqlen_k, "item") else max_seqlen_k
+
+    assert q.dtype in (torch.float16, torch.bfloat16), "FlashAttention only support fp16 and bf16 data type"
+    assert q.dtype == k.dtype
+    assert q.dtype == v.dtype
+    assert cu_seqlens_q.dtype == torch.int32
+    assert cu_seqlens_q.is_contiguous()
+    total_q, num_heads, head_size = q.size()
+    batch_size = cu_seqlens_q.numel() - 1
+    paged = block_table is not None
+    if paged:
+        assert k.dim() == 4 and k.size() == v.size()
+        num_blocks, block_size, num_heads_k = k.size(0), k.size(1), k.size(2)
+        assert k.shape == (num_blocks, block_size, num_heads_k, head_size)
+        assert block_table.dtype == torch.int32 and block_table.stride(-1) == 1
+        assert block_table.size(0) == batch_size
+    else:
+        assert k.dim() == 3 and k.size() == v.size()
+        num_blocks, block_size, num_heads_k = 0, 0, k.size(1)
+        assert k.shape[2] == head_size
+        assert cu_seqlens_k.dtype == torch.int32 and cu_seqlens_k.is_contiguous()
+        assert cu_seqlens_k.size() == (batch_size + 1,)
+    assert k.stride() == v.stride()
+    if seqused_k is not None:
+        assert seqused_k.dtype == torch.int32
+        assert seqused_k.is_contiguous()
+        assert seqused_k.size() == (batch_size,)
+    assert head_size <= 256, "FlashAttention forward only supports head dimension at most 256"
+    assert head_size % 8 == 0, "head_size must be a multiple of 8, this is ensured by padding!"
+    assert num_heads % num_heads_k == 0, "Number of heads in key/value must divide number of heads in query"
+    if out is not None:
+        assert out.stride(-1) == 1
+        assert out.dtype == q.dtype
+        assert out.size() == (total_q, num_heads, head_size)
+    else:
+        out = torch.empty_like(q)
+    if alibi_slopes is not None:
+        assert alibi_slopes.dtype == torch.float32
+        assert alibi_slopes.stride(-1) == 1
+        assert alibi_slopes.shape == (num_heads,) or alibi_slopes.shape == (batch_size, num_heads)
+    lse = torch.empty((num_heads, total_q), dtype=torch.float32, device=q.device)
+
+    p = _lib.AttnParams()
+    p.q, p.k, p.v, p.out, p.lse = q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.cu_seqlens_q = cu_seqlens_q.data_ptr()
+    p.cu_seqlens_k = _lib.ptr(cu_seqlens_k)
+    p.seqused_k = _lib.ptr(seqused_k)
+    p.block_table = _lib.ptr(block_table)
+    p.alibi_slopes = _lib.ptr(alibi_slopes)
+    p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
+    p.o_row_stride, p.o_head_stride = out.stride(0), out.stride(1)
+    if paged:
+        p.k_block_stride, p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1), k.stride(2)
+        p.v_block_stride, p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1), v.stride(2)
+        p.block_table_stride = block_table.stride(0)
+    else:
+        p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
+        p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
+    p.alibi_batch_stride = alibi_slopes.stride(0) if (alibi_slopes is not None and alibi_slopes.dim() == 2) else 0
+    p.total_q, p.batch, p.num_heads, p.num_heads_k, p.head_dim = total_q, batch_size, num_heads, num_heads_k, head_size
+    p.max_seqlen_q, p.max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
+    p.block_size, p.num_blocks = block_size, num_blocks
+    p.window_left, p.window_right = real_window_size
+    p.softmax_scale, p.softcap = float(softmax_scale), float(softcap)
+    p.causal = 1 if causal else 0
+    p.dtype = _lib.dtype_code(q.dtype)
+    p.num_splits = 0
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        nbytes = lib.fg_flash_attn_workspace_bytes(batch_size, num_heads, head_size, int(max_seqlen_q),
+                                                   int(max_seqlen_k))
+        if nbytes > 0:
+            ws = _workspace(dev, nbytes)
+            p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+        _lib.check(lib.fg_flash_attn_varlen(C.byref(p), _lib.stream_ptr(dev)))
+    return (out, lse) if return_softmax_lse else out

@@ -1,0 +1,227 @@
+/*
+ * flaggems_b200 -- C ABI of the B200 (sm_100a) LLM-inference operator path.
+ *
+ * Every entry point takes plain device pointers, sizes and strides (strides are
+ * in ELEMENTS, never bytes), a dtype code and the CUDA stream to launch on
+ * (a cudaStream_t passed as void*; NULL is the legacy default stream).  Nothing
+ * here allocates device memory unless stated otherwise and nothing synchronises the
+ * stream: the call returns once the kernels are enqueued.  The device that owns the
+ * pointers must be the current CUDA device of the calling thread.
+ *
+ * Return value: 0 on success, a negative FG_ERR_* code on failure.  After a
+ * failure fg_last_error() returns a thread-local, human readable message; the
+ * Python host layer raises it as RuntimeError, which is how the reference's
+ * C++ wrappers report errors (TORCH_CHECK -> c10::Error).
+ *
+ * Each declaration cites the reference (FlagGems v3.0) interface it replaces, by
+ * path inside the FlagGems source tree.
+ */
+#ifndef FLAGGEMS_B200_H_
+#define FLAGGEMS_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FG_API __attribute__((visibility("default")))
+
+/* dtype codes for floating-point tensors */
+enum { FG_F32 = 0, FG_F16 = 1, FG_BF16 = 2 };
+
+/* error codes */
+enum {
+  FG_OK = 0,
+  FG_ERR_INVALID = -1,     /* bad argument (shape, stride, dtype, null pointer)   */
+  FG_ERR_UNSUPPORTED = -2, /* valid in the reference, not implemented here        */
+  FG_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed                   */
+  FG_ERR_TOO_LARGE = -4    /* size exceeds a documented limit of the entry point  */
+};
+
+/* ABI version of this header; bumped on any signature change. */
+FG_API int fg_abi_version(void);
+/* Message of the last failing call made by this thread ("" if none). */
+FG_API const char* fg_last_error(void);
+/* Number of kernels this library has launched since load (all threads). Used by
+ * the benchmark to report how many of its own kernels ran in a timed region. */
+FG_API int64_t fg_launch_count(void);
+/* Device status word of the current device: 0 when healthy, otherwise the code a
+ * kernel stored when one of its bounded waits (mbarrier / TMEM hand-off) ran out of
+ * time and it returned early (101 = GEMM, 102 = attention prefill).  Synchronises
+ * with the device (a 4-byte read-back).  reset != 0 clears the word. */
+FG_API int fg_device_status(int reset);
+
+/* ------------------------------------------------------------------------
+ * fused_add_rms_norm: residual += x ; x = rmsnorm(residual) * weight, in place.
+ * Replaces flag_gems::fused_add_rms_norm (lib/fused_add_rms_norm.cpp:14-72) and
+ * the Python op src/flag_gems/fused/fused_add_rms_norm.py:57-82.
+ * x, residual: [M, N] with unit column stride and the given row strides.
+ * The sum is kept in fp32; the variance uses the unrounded sum, residual
+ * receives the sum rounded to `dtype`.
+ * ---------------------------------------------------------------------- */
+FG_API int fg_fused_add_rms_norm(void* x, void* residual, const void* weight,
+                                 int64_t M, int64_t N, int64_t x_row_stride,
+                                 int64_t r_row_stride, double eps, int dtype, void* stream);
+
+/* rms_norm without residual: out = x * rsqrt(mean(x^2) + eps) * weight.
+ * Replaces flag_gems::rms_norm (lib/rms_norm.cpp:15-72; Python
+ * src/flag_gems/ops/rms_norm.py:221). out may alias x. */
+FG_API int fg_rms_norm(const void* x, const void* weight, void* out, int64_t M, int64_t N,
+                       int64_t x_row_stride, int64_t o_row_stride, double eps, int dtype,
+                       void* stream);
+
+/* ------------------------------------------------------------------------
+ * silu_and_mul: out = silu(fp32(a)) * b, elementwise with broadcasting.
+ * Replaces silu_and_mul / silu_and_mul_out
+ * (src/flag_gems/fused/silu_and_mul.py:12-17,47-53).
+ * All three tensors are described over the same `ndim` (<= 6) broadcast shape
+ * `sizes`; a broadcast dimension has stride 0.  a, b and out share `dtype`.
+ * ---------------------------------------------------------------------- */
+FG_API int fg_silu_and_mul(const void* a, const void* b, void* out, int ndim,
+                           const int64_t* sizes, const int64_t* a_strides,
+                           const int64_t* b_strides, const int64_t* o_strides, int dtype,
+                           void* stream);
+
+/* ------------------------------------------------------------------------
+ * rotary_embedding: rotate q [T, Hq, D] and k [T, Hk, D] by cos/sin rows.
+ * Replaces flag_gems::rotary_embedding / rotary_embedding_inplace
+ * (lib/rotary_embedding.cpp:96-280) and apply_rotary_pos_emb
+ * (src/flag_gems/fused/rotary_embedding.py:181-312).
+ * q_out/k_out equal q/k for the in-place form.  cos, sin: [max_pos, D/2] with
+ * unit column stride.  positions: int64 (pos_is_i64=1) or int32 token positions,
+ * or NULL, in which case position = token % seq_len.  interleaved=0 is the
+ * NeoX (half-split) layout, 1 the GPT-J (pairwise) layout.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  void* q_out;
+  void* k_out;
+  const void* cos;
+  const void* sin;
+  const void* positions;
+  int64_t num_tokens, q_heads, k_heads, head_dim;
+  int64_t q_stride_t, q_stride_h, q_stride_d;
+  int64_t k_stride_t, k_stride_h, k_stride_d;
+  int64_t qo_stride_t, qo_stride_h, qo_stride_d;
+  int64_t ko_stride_t, ko_stride_h, ko_stride_d;
+  int64_t pos_stride, cos_stride, sin_stride;
+  int64_t seq_len;       /* used only when positions == NULL */
+  int64_t max_positions; /* rows of cos/sin; positions are clamped into [0, max_positions) */
+  int32_t pos_is_i64;
+  int32_t interleaved;
+  int32_t dtype;     /* dtype of q, k and the outputs */
+  int32_t cos_dtype; /* dtype of cos and sin */
+} fg_rope_params;
+FG_API int fg_rotary_embedding(const fg_rope_params* p, void* stream);
+
+/* ------------------------------------------------------------------------
+ * reshape_and_cache_flash: scatter new K/V tokens into a paged cache.
+ * Replaces flag_gems::reshape_and_cache_flash
+ * (lib/reshape_and_cache_flash.cpp:11-67; Python
+ * src/flag_gems/fused/reshape_and_cache_flash.py:61-112).
+ * key/value: [T, H, D] (unit stride over D, head stride D, token stride given).
+ * caches: [num_blocks, block_size, H, D] with the given block / page-row / head
+ * strides.  slot_mapping: int64 [T]; a negative slot skips the token, and so does
+ * a slot at or beyond num_blocks*block_size (the reference would write out of
+ * bounds there).  A pure byte copy: `elem_size` is 1, 2 or 4 bytes.  Bit-exact.
+ * ---------------------------------------------------------------------- */
+FG_API int fg_reshape_and_cache_flash(const void* key, const void* value, void* key_cache,
+                                      void* value_cache, const int64_t* slot_mapping,
+                                      int64_t num_tokens, int64_t num_heads,
+                                      int64_t head_size, int64_t block_size,
+                                      int64_t num_blocks, int64_t key_stride,
+                                      int64_t value_stride,
+                                      int64_t cache_block_stride, int64_t cache_row_stride,
+                                      int64_t cache_head_stride, int elem_size, void* stream);
+
+/* ------------------------------------------------------------------------
+ * gemm: C = alpha * A @ B (+ beta * bias), fp32 accumulation.
+ * Replaces flag_gems::mm_tensor / mm_out_tensor (lib/mm.cpp:239-332), addmm /
+ * addmm_out (lib/addmm.cpp:11-123) and the Python ops src/flag_gems/ops/mm.py:200-237,
+ * src/flag_gems/ops/addmm.py:83-181.
+ * A [M,K], B [K,N], C [M,N], bias broadcast to [M,N]; every tensor is given by
+ * its two element strides so row-major, column-major and stride-0 (bias) forms
+ * are all accepted.  bias == NULL means plain mm (alpha, beta ignored).
+ * The epilogue is evaluated in fp32 and rounded once to the dtype of C.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* a;
+  const void* b;
+  const void* bias;
+  void* c;
+  int64_t M, N, K;
+  int64_t a_stride0, a_stride1;
+  int64_t b_stride0, b_stride1;
+  int64_t bias_stride0, bias_stride1;
+  int64_t c_stride0, c_stride1;
+  double alpha, beta;
+  int32_t dtype; /* dtype of A, B, bias and C */
+  int32_t reserved;
+} fg_gemm_params;
+FG_API int fg_gemm(const fg_gemm_params* p, void* stream);
+/* 1 if fg_gemm would take the tcgen05/TMA path for these arguments, 0 if the
+ * generic path.  Pure host logic (no CUDA call). */
+FG_API int fg_gemm_uses_tcgen05(const fg_gemm_params* p);
+
+/* ------------------------------------------------------------------------
+ * flash_attn_varlen: FlashAttention-2 style forward over variable-length
+ * sequences with a paged or contiguous KV store.
+ * Replaces flag_gems::flash_attn_varlen_func (lib/flash_attn_varlen_func.cpp:14-578)
+ * and mha_varlan_fwd (src/flag_gems/ops/flash_api.py:230-569); the fields follow
+ * FlashFwdParams (include/flag_gems/operators.h:126-194).
+ *
+ * q, out: [total_q, Hq, D].  Paged form (block_table != NULL): k, v are
+ * [num_blocks, block_size, Hk, D] and k_len[b] = seqused_k[b].  Contiguous form
+ * (block_table == NULL): k, v are [total_k, Hk, D] and sequence b owns rows
+ * cu_seqlens_k[b] .. cu_seqlens_k[b+1]; seqused_k, when given, shortens it.
+ * The causal mask is aligned to the bottom-right corner: key j is visible to
+ * query i iff j <= i + k_len - q_len.  Rows with no visible key produce 0 and
+ * an LSE of +inf.  lse (optional) is fp32 [Hq, total_q].
+ *
+ * workspace: device scratch for split-KV decode, at least
+ * fg_flash_attn_workspace_bytes(...) bytes, or NULL to forbid splitting.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse; /* may be NULL */
+  const int32_t* cu_seqlens_q;  /* [batch+1] */
+  const int32_t* cu_seqlens_k;  /* [batch+1] or NULL */
+  const int32_t* seqused_k;     /* [batch] or NULL */
+  const int32_t* block_table;   /* [batch, max_blocks_per_seq] or NULL */
+  const float* alibi_slopes;    /* [Hq] or [batch, Hq] or NULL */
+  void* workspace;
+  int64_t workspace_bytes;
+  int64_t q_row_stride, q_head_stride;
+  int64_t k_row_stride, k_head_stride, k_block_stride;
+  int64_t v_row_stride, v_head_stride, v_block_stride;
+  int64_t o_row_stride, o_head_stride;
+  int64_t block_table_stride;
+  int64_t alibi_batch_stride;
+  int64_t total_q, batch, num_heads, num_heads_k, head_dim;
+  int64_t max_seqlen_q, max_seqlen_k;
+  int64_t block_size, num_blocks;
+  int64_t window_left, window_right; /* -1 = unbounded */
+  double softmax_scale;
+  double softcap; /* 0 = off */
+  int32_t causal;
+  int32_t dtype; /* FG_F16 or FG_BF16 */
+  int32_t num_splits; /* 0 = choose, 1 = never split, >1 = force */
+  int32_t reserved;
+} fg_attn_params;
+FG_API int fg_flash_attn_varlen(const fg_attn_params* p, void* stream);
+FG_API int64_t fg_flash_attn_workspace_bytes(int64_t batch, int64_t num_heads,
+                                             int64_t head_dim, int64_t max_seqlen_q,
+                                             int64_t max_seqlen_k);
+/* Which kernel family fg_flash_attn_varlen would pick: 0 generic (mma.sync),
+ * 1 tcgen05 prefill, 2 split-KV decode.  Pure host logic. */
+FG_API int fg_flash_attn_path(const fg_attn_params* p);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAGGEMS_B200_H_ */

@@ -1,0 +1,248 @@
+"""CPU oracle of the inference operator path -- TEST INFRASTRUCTURE, NOT PRODUCT.
+
+A restatement, in plain torch on the CPU, of the computations FlagGems' own tests use
+as ground truth for the path's operators.  Only ``tests/``, the smoke check and the
+CPU-baseline legs of ``bench.py`` may import this module; no operator of
+``flaggems_b200`` calls into it, and the product has no CPU path at all.
+
+Pinning: the FlagGems tree stores no golden vectors for these operators (each test
+draws random inputs and compares with a torch expression).  The functions below are
+therefore pinned against the reference's own test oracles *executed from the reference
+checkout*: ``tests/golden/make_golden.py`` extracts those oracle functions from the
+reference's test files, runs them on seeded inputs and stores inputs and outputs as
+fixtures; ``tests/test_oracle_golden.py`` replays the fixtures through this module.
+
+Every function cites the reference file:line it follows (paths inside the FlagGems tree).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+__all__ = [
+    "sdpa_causal",
+    "paged_attention",
+    "varlen_attention",
+    "alibi_bias",
+    "reshape_and_cache_flash",
+    "fused_add_rms_norm",
+    "rms_norm",
+    "rope_cos_sin",
+    "apply_rotary_pos_emb",
+    "silu_and_mul",
+    "mm",
+    "addmm",
+]
+
+
+# --------------------------------------------------------------------------- attention
+def sdpa_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                is_causal: bool = True) -> torch.Tensor:
+    """Dense scaled-dot-product attention ``[B, H, S, D]`` written out as masked softmax.
+
+    Follows ``torch_sdpa`` (tests/test_attention_ops.py:200-229), i.e.
+    ``F.scaled_dot_product_attention(q, k, v, scale=scale, is_causal=True)``; the
+    top-left causal mask of SDPA equals the bottom-right one when Sq == Sk."""
+    s = torch.einsum("bhqd,bhkd->bhqk", q.float(), k.float()) * scale
+    if is_causal:
+        sq, sk = q.shape[-2], k.shape[-2]
+        mask = torch.ones(sq, sk, dtype=torch.bool).tril(diagonal=0)
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("bhqk,bhkd->bhqd", p, v.float()).to(q.dtype)
+
+
+def alibi_bias(slopes: torch.Tensor, seqlen_q: int, seqlen_k: int, causal: bool) -> torch.Tensor:
+    """ALiBi bias ``[batch, heads, 1|seqlen_q, seqlen_k]`` from per-(batch, head) slopes.
+
+    Follows ``attn_bias_from_alibi_slopes`` (tests/test_attention_ops.py:804-816)."""
+    slopes = slopes.float().unsqueeze(-1).unsqueeze(-1)
+    if causal:
+        return torch.arange(-seqlen_k + 1, 1, dtype=torch.float32) * slopes
+    row = torch.arange(seqlen_q, dtype=torch.long).unsqueeze(-1)
+    col = torch.arange(seqlen_k, dtype=torch.long)
+    rel = torch.abs(row + seqlen_k - seqlen_q - col)
+    return -slopes * rel.to(slopes.dtype)
+
+
+def paged_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    query_lens: Sequence[int],
+    kv_lens: Sequence[int],
+    block_tables: torch.Tensor,
+    scale: float,
+    attn_bias: Optional[torch.Tensor] = None,
+    sliding_window: Optional[int] = None,
+    soft_cap: Optional[float] = None,
+    causal: bool = True,
+    compute_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Varlen attention over a paged KV cache, one sequence at a time.
+
+    Follows ``ref_paged_attn`` (tests/test_attention_ops.py:819-881): gather the pages
+    named by ``block_tables[i]``, repeat KV heads for GQA, scale q, bottom-right causal
+    mask ``triu(diagonal=kv_len - query_len + 1)``, optional sliding window and soft cap
+    ``cap * tanh(s / cap)``, optional additive bias, softmax, cast to the value dtype,
+    then PV.  ``compute_dtype`` (default: the input dtype, as the reference test does
+    on the device) lets the caller evaluate the same formula in fp32."""
+    num_seqs = len(query_lens)
+    bt = block_tables.cpu().numpy()
+    _, block_size, num_kv_heads, head_size = key_cache.shape
+    cd = compute_dtype or query.dtype
+    outputs: List[torch.Tensor] = []
+    start = 0
+    for i in range(num_seqs):
+        ql, kl = int(query_lens[i]), int(kv_lens[i])
+        q = query[start:start + ql].to(cd) * scale
+        nblk = (kl + block_size - 1) // block_size
+        idx = bt[i, :nblk]
+        k = key_cache[idx].view(-1, num_kv_heads, head_size)[:kl].to(cd)
+        v = value_cache[idx].view(-1, num_kv_heads, head_size)[:kl].to(cd)
+        if q.shape[1] != k.shape[1]:
+            rep = q.shape[1] // k.shape[1]
+            k = torch.repeat_interleave(k, rep, dim=1)
+            v = torch.repeat_interleave(v, rep, dim=1)
+        attn = torch.einsum("qhd,khd->hqk", q, k)
+        ones = torch.ones(ql, kl)
+        mask = torch.triu(ones, diagonal=kl - ql + 1).bool() if causal else torch.zeros(ql, kl).bool()
+        if sliding_window is not None:
+            mask |= torch.triu(ones, diagonal=kl - (ql + sliding_window) + 1).bool().logical_not()
+        if soft_cap is not None:
+            attn = soft_cap * torch.tanh(attn / soft_cap)
+        attn = attn.masked_fill(mask, float("-inf"))
+        if attn_bias is not None:
+            attn = attn + attn_bias[i, :, :ql, :kl]
+        p = torch.softmax(attn, dim=-1)
+        p = torch.nan_to_num(p, nan=0.0)  # rows with no visible key -> zeros (kernel contract)
+        out = torch.einsum("hqk,khd->qhd", p.to(v.dtype), v)
+        outputs.append(out.to(query.dtype))
+        start += ql
+    return torch.cat(outputs, dim=0)
+
+
+def varlen_attention(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+    cu_seqlens_q: torch.Tensor, cu_seqlens_k: torch.Tensor, scale: float, causal: bool = True,
+    soft_cap: Optional[float] = None, compute_dtype: Optional[torch.dtype] = None,
+) -> torch.Tensor:
+    """Contiguous varlen form: sequence i owns rows ``cu_seqlens[i]:cu_seqlens[i+1]``.
+
+    Same per-sequence formula as :func:`paged_attention`; expressed by viewing the
+    packed K/V as a one-token-per-page cache with an identity block table."""
+    cq = cu_seqlens_q.tolist()
+    ck = cu_seqlens_k.tolist()
+    qlens = [cq[i + 1] - cq[i] for i in range(len(cq) - 1)]
+    klens = [ck[i + 1] - ck[i] for i in range(len(ck) - 1)]
+    maxk = max(klens) if klens else 0
+    bt = torch.zeros((len(klens), max(maxk, 1)), dtype=torch.int32)
+    for i, kl in enumerate(klens):
+        bt[i, :kl] = torch.arange(ck[i], ck[i] + kl, dtype=torch.int32)
+    return paged_attention(q, k.unsqueeze(1), v.unsqueeze(1), qlens, klens, bt, scale,
+                           soft_cap=soft_cap, causal=causal, compute_dtype=compute_dtype)
+
+
+# --------------------------------------------------------------------------- KV cache
+def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                            value_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """``cache[slot // block_size, slot % block_size] = key[i]`` for every token, in place.
+
+    Follows the loop of tests/test_attention_ops.py:1459-1467; negative slots are
+    skipped as in the kernel (src/flag_gems/fused/reshape_and_cache_flash.py:33-35)."""
+    block_size = key_cache.shape[1]
+    blk = torch.div(slot_mapping, block_size, rounding_mode="floor").tolist()
+    off = (slot_mapping % block_size).tolist()
+    slots = slot_mapping.tolist()
+    for i in range(slot_mapping.numel()):
+        if slots[i] < 0:
+            continue
+        key_cache[blk[i], off[i], :, :] = key[i]
+        value_cache[blk[i], off[i], :, :] = value[i]
+
+
+# --------------------------------------------------------------------------- norms
+def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                       upcast: torch.dtype = torch.float64):
+    """Returns ``(normed, new_residual)`` in the upcast dtype.
+
+    Follows ``_torch_fused_add_rms_norm`` (tests/test_norm_ops.py:614-618) on inputs
+    upcast as ``to_reference(..., True)`` does (tests/accuracy_utils.py:175-186)."""
+    x = x.to(upcast) + residual.to(upcast)
+    variance = x.pow(2).mean(-1, keepdim=True)
+    hidden = x * torch.rsqrt(variance + eps)
+    return weight.to(upcast) * hidden, x
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, upcast: torch.dtype = torch.float64):
+    """``x * rsqrt(mean(x^2) + eps) * weight`` (tests/test_norm_ops.py, rms_norm oracle;
+    kernel src/flag_gems/ops/rms_norm.py:17-51)."""
+    x = x.to(upcast)
+    variance = x.pow(2).mean(-1, keepdim=True)
+    return weight.to(upcast) * (x * torch.rsqrt(variance + eps))
+
+
+# --------------------------------------------------------------------------- rope
+def rope_cos_sin(max_seq_len: int, dim: int, dtype: torch.dtype, base: float = 10000.0):
+    """cos/sin tables ``[max_seq_len, dim // 2]`` computed in fp32, then cast to ``dtype``.
+
+    Follows ``get_rope_cos_sin`` (tests/test_special_ops.py:106-112)."""
+    inv_freq = 1.0 / (base ** (torch.arange(0, dim, 2).float() / dim))
+    t = torch.arange(max_seq_len, dtype=inv_freq.dtype)
+    freqs = torch.outer(t, inv_freq)
+    return freqs.cos().to(dtype), freqs.sin().to(dtype)
+
+
+def _rotate_half(x):
+    x1 = x[..., : x.shape[-1] // 2]
+    x2 = x[..., x.shape[-1] // 2:]
+    return torch.cat((-x2, x1), dim=-1)
+
+
+def _rotate_interleave(x):
+    x1 = x[..., ::2]
+    x2 = x[..., 1::2]
+    return torch.stack((-x2, x1), dim=-1).flatten(-2)
+
+
+def apply_rotary_pos_emb(q, k, cos, sin, position_ids: Optional[torch.Tensor] = None,
+                         rotary_interleaved: bool = False, upcast: torch.dtype = torch.float32):
+    """Rotary embedding of q ``(..., seq, heads, dim)`` / k; returns upcast tensors.
+
+    Follows ``torch_apply_rotary_pos_emb`` (tests/test_special_ops.py:133-161)."""
+    q = q.to(upcast)
+    k = k.to(upcast)
+    cos = cos.to(upcast)
+    sin = sin.to(upcast)
+    if position_ids is None:
+        cos = cos[None, : q.size(-3), None, :]
+        sin = sin[None, : q.size(-3), None, :]
+    else:
+        cos = cos[position_ids].unsqueeze(-2)
+        sin = sin[position_ids].unsqueeze(-2)
+    if rotary_interleaved:
+        cos = torch.repeat_interleave(cos, 2, dim=-1)
+        sin = torch.repeat_interleave(sin, 2, dim=-1)
+        rot = _rotate_interleave
+    else:
+        cos = torch.cat([cos, cos], dim=-1)
+        sin = torch.cat([sin, sin], dim=-1)
+        rot = _rotate_half
+    return (q * cos) + (rot(q) * sin), (k * cos) + (rot(k) * sin)
+
+
+# --------------------------------------------------------------------------- pointwise / blas
+def silu_and_mul(x: torch.Tensor, y: torch.Tensor, upcast: torch.dtype = torch.float64) -> torch.Tensor:
+    """``silu(x) * y`` on upcast inputs (tests/test_binary_pointwise_ops.py:1386)."""
+    return torch.mul(torch.nn.functional.silu(x.to(upcast)), y.to(upcast))
+
+
+def mm(a: torch.Tensor, b: torch.Tensor, upcast: torch.dtype = torch.float64) -> torch.Tensor:
+    """``torch.mm`` on upcast inputs (tests/test_blas_ops.py:129-132)."""
+    return torch.mm(a.to(upcast), b.to(upcast))
+
+
+def addmm(bias, mat1, mat2, alpha=1.0, beta=1.0, upcast: torch.dtype = torch.float64) -> torch.Tensor:
+    """``torch.addmm`` on upcast inputs (tests/test_blas_ops.py:38-44)."""
+    return torch.addmm(bias.to(upcast), mat1.to(upcast), mat2.to(upcast), alpha=alpha, beta=beta)

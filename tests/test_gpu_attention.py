@@ -1,0 +1,225 @@
+"""GPU parity: flash_attn_varlen_func (paged prefill, paged decode, contiguous varlen)
+against the CPU oracle evaluated in fp32.
+
+The parameter grids follow FlagGems' tests/test_attention_ops.py:886-1085 (sequence
+mixes, head ratios, head sizes 128/192/256, ALiBi, soft-cap, fp16/bf16) with the
+reference's tolerance atol=2e-2, rtol=1e-2; further cases cover the contiguous form,
+sliding windows, empty rows, split-KV decode and the benchmark configurations."""
+import ctypes
+
+import pytest
+import torch
+
+from flaggems_b200 import _lib, workloads
+from oracle import reference_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ATOL, RTOL = 2e-2, 1e-2
+
+
+def _oracle(q, kc, vc, qlens, klens, bt, scale, **kw):
+    return O.paged_attention(q.cpu(), kc.cpu(), vc.cpu(), qlens, klens, bt.cpu(), scale,
+                             compute_dtype=torch.float32, **kw)
+
+
+def _make(seq_lens, num_heads, head_size, block_size, num_blocks, dtype, seed=1234567890):
+    torch.manual_seed(seed)
+    qlens = [x[0] for x in seq_lens]
+    klens = [x[1] for x in seq_lens]
+    hq, hk = num_heads
+    q = torch.randn(sum(qlens), hq, head_size, dtype=dtype, device=DEV)
+    kc = torch.randn(num_blocks, block_size, hk, head_size, dtype=dtype, device=DEV)
+    vc = torch.randn_like(kc)
+    cu = torch.tensor([0] + qlens, dtype=torch.int32).cumsum(0, dtype=torch.int32).to(DEV)
+    used = torch.tensor(klens, dtype=torch.int32, device=DEV)
+    maxb = (max(klens) + block_size - 1) // block_size
+    bt = torch.randint(0, num_blocks, (len(seq_lens), maxb), dtype=torch.int32, device=DEV)
+    return q, kc, vc, cu, used, bt, qlens, klens
+
+
+@pytest.mark.parametrize("seq_lens", [[(1, 1328), (5, 18), (129, 463)]])
+@pytest.mark.parametrize("num_heads", [(4, 4), (8, 2), (16, 2)])
+@pytest.mark.parametrize("head_size", [128, 192, 256])
+@pytest.mark.parametrize("block_size", [32])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("alibi", [False, True])
+@pytest.mark.parametrize("soft_cap", [None, 10.0, 50.0])
+@pytest.mark.parametrize("num_blocks", [2048])
+def test_flash_attn_varlen_func(fg, seq_lens, num_heads, head_size, block_size, dtype, alibi, soft_cap, num_blocks):
+    if alibi and soft_cap is not None:
+        pytest.skip("combination excluded by the reference test (numerical stability)")
+    q, kc, vc, cu, used, bt, qlens, klens = _make(seq_lens, num_heads, head_size, block_size, num_blocks, dtype)
+    scale = head_size ** -0.5
+    slopes = bias = None
+    if alibi:
+        slopes = torch.ones(len(seq_lens), num_heads[0], dtype=torch.float32, device=DEV) * 0.3
+        bias = O.alibi_bias(slopes.cpu(), max(qlens), max(klens), causal=True)
+    out = fg.flash_attn_varlen_func(
+        q=q, k=kc, v=vc, cu_seqlens_q=cu, seqused_k=used, max_seqlen_q=max(qlens), max_seqlen_k=max(klens),
+        softmax_scale=scale, causal=True, window_size=(-1, -1), block_table=bt,
+        softcap=soft_cap if soft_cap is not None else 0, alibi_slopes=slopes, fa_version=2)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, scale, attn_bias=bias, soft_cap=soft_cap)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+
+
+@pytest.mark.parametrize("seq_lens", [[(1, 1328), (1, 18), (1, 463)]])
+@pytest.mark.parametrize("num_heads", [(8, 2), (32, 8), (4, 4)])
+@pytest.mark.parametrize("head_size", [128, 64, 256])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("soft_cap", [None, 10.0])
+def test_flash_attn_varlen_func_decode(fg, seq_lens, num_heads, head_size, dtype, soft_cap):
+    q, kc, vc, cu, used, bt, qlens, klens = _make(seq_lens, num_heads, head_size, 32, 2048, dtype)
+    scale = head_size ** -0.5
+    out, lse = fg.flash_attn_varlen_func(
+        q=q, k=kc, v=vc, cu_seqlens_q=cu, seqused_k=used, max_seqlen_q=1, max_seqlen_k=max(klens),
+        softmax_scale=scale, causal=True, window_size=(-1, -1), block_table=bt,
+        softcap=soft_cap if soft_cap is not None else 0, fa_version=2, return_softmax_lse=True)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, scale, soft_cap=soft_cap)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    assert lse.shape == (num_heads[0], len(seq_lens)) and torch.isfinite(lse).all()
+
+
+def _params_for(q, kc, vc, cu, used, bt, max_q, max_k):
+    p = _lib.AttnParams()
+    p.q, p.k, p.v, p.out = q.data_ptr(), kc.data_ptr(), vc.data_ptr(), q.data_ptr()
+    p.cu_seqlens_q, p.seqused_k, p.block_table = cu.data_ptr(), used.data_ptr(), bt.data_ptr()
+    p.total_q, p.batch, p.num_heads, p.head_dim = q.shape[0], cu.numel() - 1, q.shape[1], q.shape[2]
+    p.num_heads_k = kc.shape[2]
+    p.max_seqlen_q, p.max_seqlen_k = max_q, max_k
+    p.block_size, p.num_blocks = kc.shape[1], kc.shape[0]
+    p.window_left = p.window_right = -1
+    p.causal, p.dtype = 1, _lib.dtype_code(q.dtype)
+    return p
+
+
+def test_decode_takes_the_split_kv_path_and_lse_is_right(fg):
+    seq_lens = [(1, 5000), (1, 64), (1, 1), (1, 777)]
+    q, kc, vc, cu, used, bt, qlens, klens = _make(seq_lens, (32, 8), 128, 16, 4096, torch.bfloat16)
+    assert _lib.load().fg_flash_attn_path(ctypes.byref(_params_for(q, kc, vc, cu, used, bt, 1, 5000))) == 2
+    scale = 128 ** -0.5
+    out, lse = fg.flash_attn_varlen_func(q, kc, vc, 1, cu, 5000, seqused_k=used, softmax_scale=scale, causal=True,
+                                         block_table=bt, return_softmax_lse=True)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, scale)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    # lse[h, t] = logsumexp_j(scale * q.k)
+    for i, (kl, row) in enumerate(zip(klens, bt.cpu())):
+        nb = (kl + 15) // 16
+        k = kc[row[:nb].long().to(DEV)].reshape(-1, 8, 128)[:kl].float().repeat_interleave(4, dim=1)
+        s = torch.einsum("hd,khd->hk", q[i].float(), k) * scale
+        torch.testing.assert_close(lse[:, i].cpu(), torch.logsumexp(s, dim=-1).cpu(), atol=2e-3, rtol=2e-3)
+
+
+def test_contiguous_varlen_windows_and_empty_rows(fg):
+    b = workloads.prefill_batch(seed=7, num_seqs=5, min_len=1, max_len=300, q_heads=8, kv_heads=2, head_dim=128,
+                                block_size=16, dtype=torch.float16, device=DEV)
+    ref = _oracle(b.q, b.key_cache, b.value_cache, b.query_lens, b.kv_lens, b.block_table, b.scale)
+    paged = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                      seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+    contig = fg.flash_attn_varlen_func(b.q, b.k, b.v, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                       cu_seqlens_k=b.cu_seqlens_k, causal=True)
+    torch.testing.assert_close(paged.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    torch.testing.assert_close(contig.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    # sliding window (left) with causal
+    win = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                    seqused_k=b.seqused_k, causal=True, window_size=(37, 0), block_table=b.block_table)
+    refw = _oracle(b.q, b.key_cache, b.value_cache, b.query_lens, b.kv_lens, b.block_table, b.scale,
+                   sliding_window=37 + 1)
+    # oracle's sliding_window counts the diagonal: window_left = sliding_window - 1
+    torch.testing.assert_close(win.cpu().float(), refw.float(), atol=ATOL, rtol=RTOL)
+    # non-causal
+    nc = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                   seqused_k=b.seqused_k, causal=False, block_table=b.block_table)
+    refn = _oracle(b.q, b.key_cache, b.value_cache, b.query_lens, b.kv_lens, b.block_table, b.scale, causal=False)
+    torch.testing.assert_close(nc.cpu().float(), refn.float(), atol=ATOL, rtol=RTOL)
+    # q longer than k: the first q_len - k_len rows see no key -> zeros, lse = +inf
+    seq_lens = [(70, 20), (3, 3)]
+    q, kc, vc, cu, used, bt, qlens, klens = _make(seq_lens, (4, 2), 64, 16, 64, torch.bfloat16)
+    out, lse = fg.flash_attn_varlen_func(q, kc, vc, 70, cu, 20, seqused_k=used, causal=True, block_table=bt,
+                                         return_softmax_lse=True)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, 64 ** -0.5)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    assert not out[:50].any() and torch.isinf(lse[:, :50]).all() and torch.isfinite(lse[:, 50:]).all()
+
+
+def test_golden_paged_attention_and_custom_op(fg, golden_dir):
+    for c in torch.load(golden_dir / "golden_paged_attn.pt", weights_only=False):
+        q, kc, vc = c["q"].to(DEV), c["key_cache"].to(DEV), c["value_cache"].to(DEV)
+        cu = torch.tensor([0] + c["query_lens"], dtype=torch.int32).cumsum(0, dtype=torch.int32).to(DEV)
+        used = torch.tensor(c["kv_lens"], dtype=torch.int32, device=DEV)
+        slopes = None if c["alibi_slopes"] is None else c["alibi_slopes"].to(DEV)
+        out, lse = torch.ops.flag_gems.flash_attn_varlen_func(
+            q, kc, vc, max(c["query_lens"]), cu, max(c["kv_lens"]), None, used, None, 0.0, c["scale"], True, None,
+            c["soft_cap"] or 0.0, slopes, False, False, c["block_tables"].to(DEV), False, None)
+        torch.testing.assert_close(out.cpu().float(), c["out"].float(), atol=ATOL, rtol=RTOL, msg=c["name"])
+
+
+def test_argument_errors(fg):
+    q, kc, vc, cu, used, bt, qlens, klens = _make([(4, 40)], (4, 2), 64, 16, 16, torch.bfloat16)
+    with pytest.raises(AssertionError, match="cu_seqlens_k or seqused_k"):
+        fg.flash_attn_varlen_func(q, kc, vc, 4, cu, 40, block_table=bt)
+    with pytest.raises(RuntimeError, match="Only FA2"):
+        fg.flash_attn_varlen_func(q, kc, vc, 4, cu, 40, seqused_k=used, block_table=bt, fa_version=3)
+    with pytest.raises(RuntimeError, match="num_splits"):
+        fg.flash_attn_varlen_func(q, kc, vc, 4, cu, 40, seqused_k=used, block_table=bt, num_splits=2)
+    with pytest.raises(AssertionError):
+        fg.flash_attn_varlen_func(q.float(), kc.float(), vc.float(), 4, cu, 40, seqused_k=used, block_table=bt)
+    # max_seqlen given as tensors is accepted (one host sync, as in the reference)
+    out = fg.flash_attn_varlen_func(q, kc, vc, torch.tensor(4), cu, torch.tensor(40), seqused_k=used, causal=True,
+                                    block_table=bt)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, 64 ** -0.5)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+
+
+def test_prefill_config3_reduced_and_out_argument(fg):
+    # config-3 structure (16 seqs, 32/8 heads, d 128, bf16) at lengths the CPU oracle handles
+    b = workloads.prefill_batch(seed=11, num_seqs=16, min_len=16, max_len=400, device=DEV)
+    ref = _oracle(b.q, b.key_cache, b.value_cache, b.query_lens, b.kv_lens, b.block_table, b.scale)
+    out = torch.empty_like(b.q)
+    ret = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                    seqused_k=b.seqused_k, causal=True, block_table=b.block_table, out=out)
+    assert ret is out
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    contig = fg.flash_attn_varlen_func(b.q, b.k, b.v, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                       cu_seqlens_k=b.cu_seqlens_k, causal=True)
+    torch.testing.assert_close(contig.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+
+
+def test_prefill_config3_full_size_properties(fg):
+    # Full config 3 (lengths up to 4096): oracle on the two shortest sequences, plus
+    # size-independent properties: paged == contiguous, and softmax rows are convex
+    # combinations (|out| <= max |v| per head-dim column).
+    b = workloads.prefill_batch(seed=0, device=DEV)
+    paged = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                      seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+    contig = fg.flash_attn_varlen_func(b.q, b.k, b.v, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                       cu_seqlens_k=b.cu_seqlens_k, causal=True)
+    torch.testing.assert_close(paged.float(), contig.float(), atol=ATOL, rtol=RTOL)
+    assert torch.isfinite(paged).all()
+    assert paged.float().abs().max() <= b.v.float().abs().max() + 1e-2
+    cu = b.cu_seqlens_q.cpu().tolist()
+    order = sorted(range(len(b.query_lens)), key=lambda i: b.query_lens[i])[:2]
+    for i in order:
+        sl = slice(cu[i], cu[i + 1])
+        ref = O.varlen_attention(b.q[sl].cpu(), b.k[sl].cpu(), b.v[sl].cpu(),
+                                 torch.tensor([0, cu[i + 1] - cu[i]]), torch.tensor([0, cu[i + 1] - cu[i]]), b.scale,
+                                 compute_dtype=torch.float32)
+        torch.testing.assert_close(paged[sl].cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    # the first token of every sequence attends only to itself: out == v (per KV group)
+    first = b.cu_seqlens_q[:-1].long()
+    torch.testing.assert_close(paged[first].float(), b.v[first].repeat_interleave(4, dim=1).float(), atol=1e-2, rtol=1e-2)
+
+
+def test_decode_config4_reduced_with_cache_write(fg):
+    # config-4 structure: write the new token with reshape_and_cache_flash, then decode
+    b = workloads.decode_batch(seed=5, batch=24, min_ctx=30, max_ctx=2100, device=DEV)
+    fg.reshape_and_cache_flash(b.new_key, b.new_value, b.key_cache, b.value_cache, b.slot_mapping, "auto", None, None)
+    kc_ref, vc_ref = b.key_cache.cpu().clone(), b.value_cache.cpu().clone()
+    out = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, 1, b.cu_seqlens_q, b.max_seqlen_k,
+                                    seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+    ref = O.paged_attention(b.q.cpu(), kc_ref, vc_ref, b.query_lens, b.kv_lens, b.block_table.cpu(), b.scale,
+                            compute_dtype=torch.float32)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    # the last key of each context is the token just written
+    last = b.slot_mapping
+    assert torch.equal(b.key_cache.view(-1, 8, 128)[last], b.new_key)

@@ -1,0 +1,166 @@
+"""Host-side logic that needs no GPU: registration filter, the enable()/use_gems() API
+surface, custom-op schemas, kernel-path selection, shard helpers and the no-fallback rule."""
+import ctypes
+import logging
+
+import pytest
+import torch
+
+import flaggems_b200 as fg
+from flaggems_b200 import _lib, custom_ops, dist as fdist
+from flaggems_b200.register import Register
+
+
+class _FakeLib:
+    def __init__(self):
+        self.calls = []
+
+    def impl(self, key, fn, dispatch_key):
+        self.calls.append((key, fn.__name__, dispatch_key))
+
+
+def test_register_filters_unused_and_native_keys():
+    cfg = (("mm", fg.mm), ("mm.out", fg.mm_out), ("addmm", fg.addmm), ("addmm.out", fg.addmm_out))
+    lib = _FakeLib()
+    r = Register(cfg, user_unused_ops_list=["mm"], cpp_patched_ops_list=["addmm.out"], lib=lib)
+    assert r.get_all_ops() == ["mm.out", "addmm"]
+    assert lib.calls == [("mm.out", "mm_out", "CUDA"), ("addmm", "addmm", "CUDA")]
+    assert r.get_unused_ops() == ["mm"] and r.get_vendor_name() == "nvidia" and r.get_current_device() == "cuda"
+
+
+def test_enable_and_use_gems_surface(tmp_path):
+    assert fg.device == "cuda" and fg.vendor_name == "nvidia" and fg.__version__.startswith("3.0")
+    lib = _FakeLib()
+    log = tmp_path / "oplist.log"
+    fg.enable(lib=lib, unused=["addmm_out"], record=True, once=True, path=str(log))
+    assert fg.all_ops() == ["addmm", "mm", "mm.out"]
+    logging.getLogger("flag_gems.ops").debug("GEMS TEST RECORD")
+    fg.logging_utils.teardown_flaggems_logging()
+    assert "GEMS TEST RECORD" in log.read_text()
+    # the scoped form registers on a private Library and destroys it on exit; CPU
+    # tensors are untouched by CUDA-key overrides
+    with fg.use_gems():
+        assert set(fg.all_ops()) == {"mm", "mm.out", "addmm", "addmm.out"}
+        a = torch.randn(3, 4)
+        torch.testing.assert_close(torch.mm(a, a.t()), a @ a.t())
+    for name in ("flash_attn_varlen_func", "reshape_and_cache_flash", "fused_add_rms_norm", "apply_rotary_pos_emb",
+                 "silu_and_mul", "silu_and_mul_out", "mm", "mm_out", "addmm", "addmm_out", "GemsRMSNorm", "GemsRope",
+                 "GemsSiluAndMul", "apply_gems_patches_to_vllm", "gems_rms_forward", "gems_rope_forward"):
+        assert callable(getattr(fg, name)), name
+    assert callable(fg.ops.flash_attn_varlen_func) and callable(fg.testing.assert_close)
+
+
+def test_custom_op_schemas_match_the_reference_strings():
+    for name in ("fused_add_rms_norm", "rotary_embedding_inplace", "rotary_embedding", "reshape_and_cache_flash",
+                 "flash_attn_varlen_func", "mm", "addmm", "rms_norm"):
+        op = getattr(torch.ops.flag_gems, name)
+        schema = str(op.default._schema)
+        assert schema.startswith(f"flag_gems::{name}(")
+    s = str(torch.ops.flag_gems.flash_attn_varlen_func.default._schema)
+    assert "SymInt max_seqlen_q, Tensor cu_seqlens_q, SymInt max_seqlen_k" in s and "SymInt fa_version=2" in s
+    s = str(torch.ops.flag_gems.reshape_and_cache_flash.default._schema)
+    assert "Tensor(a!) key_cache, Tensor(b!) value_cache" in s and "str kv_cache_dtype" in s
+    far = torch.ops.flag_gems.fused_add_rms_norm.default._schema
+    assert [a.name for a in far.arguments] == ["input", "residual", "weight", "epsilon"]
+    assert [bool(a.alias_info and a.alias_info.is_write) for a in far.arguments] == [True, True, False, False]
+    assert len(far.returns) == 0
+    assert set(custom_ops.SCHEMAS) == set(custom_ops._IMPLS)
+
+
+def test_no_cpu_fallback():
+    x = torch.randn(4, 8)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        fg.fused_add_rms_norm(x, x.clone(), [8], torch.ones(8))
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        fg.silu_and_mul(x, x)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        fg.mm(x, x.t())
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        fg.reshape_and_cache_flash(torch.zeros(1, 1, 8), torch.zeros(1, 1, 8), torch.zeros(1, 4, 1, 8),
+                                   torch.zeros(1, 4, 1, 8), torch.zeros(1, dtype=torch.long), "auto", None, None)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setenv("FLAGGEMS_B200_LIB", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(_lib, "_LIB", None)
+    with pytest.raises(RuntimeError, match="missing"):
+        _lib.load()
+
+
+def _gemm_params(M, N, K, dtype=_lib.FG_BF16, a_strides=None, b_strides=None, base=0x7f0000000000):
+    p = _lib.GemmParams()
+    p.a, p.b, p.c = base, base + (1 << 30), base + (2 << 30)
+    p.M, p.N, p.K = M, N, K
+    p.a_stride0, p.a_stride1 = a_strides or (K, 1)
+    p.b_stride0, p.b_stride1 = b_strides or (N, 1)
+    p.c_stride0, p.c_stride1 = N, 1
+    p.dtype = dtype
+    return p
+
+
+def test_gemm_path_selection_is_pure_host_logic():
+    uses = lambda p: _lib.load().fg_gemm_uses_tcgen05(ctypes.byref(p))
+    assert uses(_gemm_params(8192, 6144, 4096)) == 1
+    assert uses(_gemm_params(8192, 6144, 4096, b_strides=(1, 4096))) == 1       # column-major B
+    assert uses(_gemm_params(8192, 6144, 4096, a_strides=(1, 8192))) == 1       # column-major A
+    assert uses(_gemm_params(8192, 6144, 4096, dtype=_lib.FG_F32)) == 0         # fp32: CUDA-core path
+    assert uses(_gemm_params(495, 5333, 71)) == 0                               # rows not 16-byte multiples
+    assert uses(_gemm_params(1, 1, 32)) == 0
+    assert uses(_gemm_params(8192, 6144, 4096, base=0x7f0000000002)) == 0       # misaligned base
+
+
+def test_attention_path_selection():
+    def params(max_q, batch, total_q, hq=32, hk=8, d=128, alibi=False, wl=-1):
+        p = _lib.AttnParams()
+        p.max_seqlen_q, p.max_seqlen_k, p.batch, p.total_q = max_q, 4096, batch, total_q
+        p.num_heads, p.num_heads_k, p.head_dim = hq, hk, d
+        p.window_left, p.window_right = wl, -1
+        p.alibi_slopes = 0x1000 if alibi else None
+        p.causal, p.dtype = 1, _lib.FG_BF16
+        return p
+    path = lambda p: _lib.load().fg_flash_attn_path(ctypes.byref(p))
+    assert path(params(1, 256, 256)) == 2            # single-token decode -> split-KV kernel
+    assert path(params(1, 256, 256, alibi=True)) == 0
+    assert path(params(1, 256, 256, wl=128)) == 0
+    assert path(params(1, 256, 256, hq=64, hk=2)) == 0   # 32 query heads per KV head exceed one MMA tile
+    assert path(params(4096, 16, 30000)) in (0, 1)
+    ws = _lib.load().fg_flash_attn_workspace_bytes
+    assert ws(256, 32, 128, 1, 8192) == 32 * 256 * 32 * 129 * 4
+    assert ws(256, 32, 128, 1, 200) == 0 and ws(16, 32, 128, 4096, 4096) == 0
+
+
+def test_shard_helpers():
+    assert [fdist.shard_range(10, r, 4) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    qs, ks = fdist.kv_head_shard(32, 8, 3, 4)
+    assert (qs.start, qs.stop, ks.start, ks.stop) == (24, 32, 6, 8)
+    with pytest.raises(ValueError):
+        fdist.kv_head_shard(32, 8, 0, 3)
+    w = torch.arange(24.0).reshape(2, 12).repeat(1, 4)  # [2, 48]
+    parts = [fdist.column_shard(w, torch.arange(48.0), r, 2) for r in range(2)]
+    assert torch.equal(torch.cat([p[0] for p in parts], dim=1), w)
+    assert torch.equal(torch.cat([p[1] for p in parts]), torch.arange(48.0))
+    with pytest.raises(ValueError):
+        fdist.column_shard(torch.zeros(2, 20), None, 0, 2)
+    assert fdist.all_gather_columns(w, 1) is w
+
+
+def test_workload_generators_are_seeded_and_consistent():
+    from flaggems_b200 import workloads
+
+    a = workloads.prefill_batch(seed=9, num_seqs=4, min_len=3, max_len=60, q_heads=4, kv_heads=2, head_dim=16,
+                                block_size=8, dtype=torch.float32, device="cpu")
+    b = workloads.prefill_batch(seed=9, num_seqs=4, min_len=3, max_len=60, q_heads=4, kv_heads=2, head_dim=16,
+                                block_size=8, dtype=torch.float32, device="cpu")
+    assert a.query_lens == b.query_lens and torch.equal(a.q, b.q) and torch.equal(a.block_table, b.block_table)
+    # the paged cache holds exactly the packed K/V rows
+    cu = a.cu_seqlens_q.tolist()
+    for i, n in enumerate(a.kv_lens):
+        pages = a.block_table[i, : (n + 7) // 8].long()
+        rows = a.key_cache[pages].reshape(-1, 2, 16)[:n]
+        assert torch.equal(rows, a.k[cu[i]:cu[i + 1]])
+    d = workloads.decode_batch(seed=9, batch=5, min_ctx=9, max_ctx=70, q_heads=4, kv_heads=2, head_dim=16,
+                               block_size=8, dtype=torch.float32, device="cpu")
+    for i, n in enumerate(d.kv_lens):
+        assert d.slot_mapping[i] == d.block_table[i, (n - 1) // 8] * 8 + (n - 1) % 8
+    assert len(set(d.block_table[d.block_table > 0].tolist())) == int((d.block_table > 0).sum())  # disjoint pages
+    assert workloads.prefill_flops([4], q_heads=1, head_dim=1) == 4 * 10
