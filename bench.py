@@ -1,0 +1,459 @@
+#!/usr/bin/env python
+"""Benchmark of the inference operator path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One *step* is one pass of the operator path over one batch of seeded synthetic input at
+the benchmark configuration sizes: fused_add_rms_norm, rotary_embedding and silu_and_mul
+on the T=4096 Llama block, varlen causal GQA prefill (16 sequences, 128..4096 tokens),
+reshape_and_cache_flash + paged decode (batch 256, contexts 512..8192), and mm / addmm at
+the four Llama-3-8B projection shapes with M=8192.  The headline value is operator
+invocations per second; every operator's own figure (TFLOP/s or GB/s against the measured
+B200 roofline) is in ``per_op``.
+
+Under ``torchrun`` (N > 1) every rank runs the same step on its own batch of sequences
+(no exchange), and the projections become column-parallel: each rank multiplies by its
+own column shard and the shards are all-gathered over NVLink with NCCL on a side stream
+(weak scaling: fixed work per GPU).
+
+``--impl reference`` times the CPU oracle (torch CPU restatement of the reference's test
+oracles) on the host cores on a bounded sample of the same step.
+
+Rank 0 prints exactly one JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "inference operator-path throughput (fused_add_rms_norm, rope, silu_and_mul, varlen prefill, " \
+         "cache write + paged decode, mm/addmm at the benchmark configs)"
+UNIT = "ops/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ts, line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                clk, mx = float(parts[0]), float(parts[1])
+            except ValueError:
+                continue
+            smax = mx
+            if t0 - 0.05 <= ts <= t1 + 0.15:
+                sm.append(clk)
+                for n, v in zip(names, parts[4:8]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+        if not sm:  # region shorter than one sample: use whatever was seen
+            sm = [float(l.split(",")[0]) for _, l in self.lines if l and l[0].isdigit()]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- workload
+class Step:
+    """The operators of one step with their inputs resident on ``device``."""
+
+    def __init__(self, device, rank: int, world: int, seed: int = 0):
+        import flaggems_b200 as fg
+        from flaggems_b200 import workloads as W
+
+        self.fg, self.W = fg, W
+        self.device, self.rank, self.world = device, rank, world
+        s = seed + 1000 * rank  # every rank owns a different batch of sequences
+        self.x, self.res, self.w, self.eps = W.norm_inputs(seed=s + 1, device=device)
+        self.q, self.k, self.cos, self.sin, self.pos = W.rope_inputs(seed=s + 2, device=device)
+        self.act = W.silu_inputs(seed=s + 3, device=device)
+        self.half = self.act.shape[1] // 2
+        self.silu_out = torch.empty((self.act.shape[0], self.half), dtype=self.act.dtype, device=device)
+        self.pre = W.prefill_batch(seed=s + 4, device=device)
+        self.pre_out = torch.empty_like(self.pre.q)
+        self.dec = W.decode_batch(seed=s + 5, device=device)
+        self.dec_out = torch.empty_like(self.dec.q)
+        # projections: A replicated (same seed on every rank), B/bias = this rank's column shard
+        self.gemm = {}
+        for i, name in enumerate(W.GEMM_SHAPES):
+            a, b, bias = W.gemm_inputs(name, seed=seed + 10 + i, device=device)
+            if world > 1:  # the shard of a [K, N * world] weight owned by this rank
+                _, b, bias = W.gemm_inputs(name, seed=seed + 10 + i + 100 * (rank + 1), device=device)
+            c = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=device)
+            gathered = None
+            if world > 1:
+                gathered = torch.empty((world * a.shape[0], b.shape[1]), dtype=a.dtype, device=device)
+            self.gemm[name] = (a, b, bias, c, gathered)
+        self.comm_stream = torch.cuda.Stream(device=device) if world > 1 else None
+        self.ops = self._build_ops()
+
+    # each entry: (name, callable, work, kind) with kind "hbm" (bytes) or "tensor" (flops)
+    def _build_ops(self):
+        fg, W = self.fg, self.W
+        T, H = self.x.shape
+        ops = []
+        ops.append(("fused_add_rms_norm", lambda: fg.fused_add_rms_norm(self.x, self.res, [H], self.w, self.eps),
+                    4 * T * H * 2 + H * 2, "hbm"))
+        tq, hq, d = self.q.shape
+        hk = self.k.shape[1]
+        ops.append(("rotary_embedding",
+                    lambda: fg.apply_rotary_pos_emb(self.q, self.k, self.cos, self.sin, self.pos, False, True),
+                    2 * (tq * hq * d + tq * hk * d) * 2 + tq * 2 * (d // 2) * 2 + tq * 8, "hbm"))
+        a1, a2 = self.act[:, :self.half], self.act[:, self.half:]
+        ops.append(("silu_and_mul", lambda: fg.silu_and_mul_out(a1, a2, self.silu_out),
+                    self.act.numel() * 2 + self.silu_out.numel() * 2, "hbm"))
+        p = self.pre
+        ops.append(("flash_attn_varlen_func[prefill]",
+                    lambda: fg.flash_attn_varlen_func(p.q, p.key_cache, p.value_cache, p.max_seqlen_q, p.cu_seqlens_q,
+                                                      p.max_seqlen_k, seqused_k=p.seqused_k, causal=True,
+                                                      block_table=p.block_table, out=self.pre_out),
+                    W.prefill_flops(p.query_lens), "tensor"))
+        dd = self.dec
+        nk = dd.new_key.numel() * 2
+        ops.append(("reshape_and_cache_flash",
+                    lambda: fg.reshape_and_cache_flash(dd.new_key, dd.new_value, dd.key_cache, dd.value_cache,
+                                                       dd.slot_mapping, "auto", None, None),
+                    4 * nk + dd.slot_mapping.numel() * 8, "hbm"))
+        ops.append(("flash_attn_varlen_func[decode]",
+                    lambda: fg.flash_attn_varlen_func(dd.q, dd.key_cache, dd.value_cache, 1, dd.cu_seqlens_q,
+                                                      dd.max_seqlen_k, seqused_k=dd.seqused_k, causal=True,
+                                                      block_table=dd.block_table, out=self.dec_out),
+                    W.decode_bytes(dd.kv_lens, len(dd.kv_lens)), "hbm"))
+        for name, (a, b, bias, c, gathered) in self.gemm.items():
+            M, K = a.shape
+            N = b.shape[1]
+            if name in ("qkv", "gate_up"):  # qkv and gate_up carry a bias in the benchmark (addmm), o/down are mm
+                ops.append((f"addmm[{name}]", self._gemm_call(name, True), M * N * (2 * K + 1), "tensor"))
+            else:
+                ops.append((f"mm[{name}]", self._gemm_call(name, False), 2 * M * N * K, "tensor"))
+        return ops
+
+    def _gemm_call(self, name, with_bias):
+        fg = self.fg
+        a, b, bias, c, gathered = self.gemm[name]
+
+        def run():
+            if with_bias:
+                fg.addmm_out(bias, a, b, out=c)
+            else:
+                fg.mm_out(a, b, out=c)
+            if self.world > 1:
+                # column-parallel: gather the shards on the side stream; the next operators
+                # of the step overlap with the transfer, the step ends when all gathers have landed
+                self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(self.comm_stream):
+                    torch.distributed.all_gather_into_tensor(gathered, c)
+        return run
+
+    def run(self, events=None):
+        for i, (_, fn, _, _) in enumerate(self.ops):
+            if events is not None:
+                events[i][0].record()
+            fn()
+            if events is not None:
+                events[i][1].record()
+        if self.comm_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+
+    # ---------------- end-to-end form: host buffers in, host buffers out
+    def make_e2e(self):
+        """Pinned host copies of the per-step activations and host buffers for the results.
+        Weights, cos/sin tables and the paged KV cache are resident state (they are not
+        inputs of a step in serving); everything a step consumes or produces crosses PCIe."""
+        dd, p = self.dec, self.pre
+        ins = [self.x, self.res, self.q, self.k, self.pos, self.act, p.q, dd.q, dd.new_key, dd.new_value,
+               dd.slot_mapping] + [self.gemm[n][0] for n in self.gemm]
+        outs = [self.x, self.res, self.q, self.k, self.silu_out, self.pre_out, self.dec_out] + \
+               [self.gemm[n][3] for n in self.gemm]
+        self.h_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in ins]
+        self.h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
+        self.e2e_in, self.e2e_out = ins, outs
+        h2d = sum(t.numel() * t.element_size() for t in ins)
+        d2h = sum(t.numel() * t.element_size() for t in outs)
+        return h2d, d2h
+
+    def run_e2e(self):
+        for h, d in zip(self.h_in, self.e2e_in):
+            d.copy_(h, non_blocking=True)
+        self.run()
+        for h, d in zip(self.h_out, self.e2e_out):
+            h.copy_(d, non_blocking=True)
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_step_sample(seed=0):
+    """Time the CPU oracle on a bounded sample of one step; returns (scaled seconds for a
+    full step, number of ops, description).  Each operator is timed on a slice and scaled
+    by its algorithmic work."""
+    from flaggems_b200 import workloads as W
+    from oracle import reference_oracle as O  # CPU baseline leg
+
+    total = 0.0
+    detail = {}
+
+    def timed(fn):
+        t0 = time.perf_counter()
+        fn()
+        return time.perf_counter() - t0
+
+    x, r, w, eps = W.norm_inputs(seed=seed + 1, T=1024, device="cpu")
+    t = timed(lambda: O.fused_add_rms_norm(x, r, w, eps, upcast=torch.float32)) * 4
+    detail["fused_add_rms_norm"] = t
+    q, k, cos, sin, pos = W.rope_inputs(seed=seed + 2, T=1024, device="cpu")
+    cos4, sin4 = W.rope_tables(4096, 128, torch.bfloat16, "cpu")
+    t = timed(lambda: O.apply_rotary_pos_emb(q, k, cos4, sin4, pos)) * 4
+    detail["rotary_embedding"] = t
+    act = W.silu_inputs(seed=seed + 3, T=512, device="cpu")
+    h = act.shape[1] // 2
+    t = timed(lambda: O.silu_and_mul(act[:, :h], act[:, h:], upcast=torch.float32)) * 8
+    detail["silu_and_mul"] = t
+    # prefill: one 512-token sequence, scaled by FLOPs to the 16-sequence batch
+    g = torch.Generator().manual_seed(seed + 4)
+    lens = torch.randint(128, 4097, (16,), generator=g).tolist()
+    pb = W.prefill_batch(seed=seed + 4, num_seqs=1, min_len=512, max_len=512, device="cpu")
+    t1 = timed(lambda: O.paged_attention(pb.q, pb.key_cache, pb.value_cache, pb.query_lens, pb.kv_lens, pb.block_table,
+                                         pb.scale, compute_dtype=torch.float32))
+    detail["flash_attn_varlen_func[prefill]"] = t1 * W.prefill_flops(lens) / W.prefill_flops([512])
+    # decode: 4 sequences with 2048-token contexts, scaled by context tokens
+    db = W.decode_batch(seed=seed + 5, batch=4, min_ctx=2048, max_ctx=2048, device="cpu")
+    g = torch.Generator().manual_seed(seed + 5)
+    ctx = torch.randint(512, 8193, (256,), generator=g).tolist()
+    kc, vc = db.key_cache.clone(), db.value_cache.clone()
+    t0 = timed(lambda: O.reshape_and_cache_flash(db.new_key, db.new_value, kc, vc, db.slot_mapping))
+    detail["reshape_and_cache_flash"] = t0 * 256 / 4
+    t1 = timed(lambda: O.paged_attention(db.q, db.key_cache, db.value_cache, db.query_lens, db.kv_lens,
+                                         db.block_table, db.scale, compute_dtype=torch.float32))
+    detail["flash_attn_varlen_func[decode]"] = t1 * sum(ctx) / (4 * 2048)
+    # projections: 128 of the 8192 rows
+    for i, name in enumerate(W.GEMM_SHAPES):
+        a, b, bias = W.gemm_inputs(name, seed=seed + 10 + i, M=128, device="cpu")
+        if name in ("qkv", "gate_up"):
+            t = timed(lambda: O.addmm(bias, a, b, upcast=torch.float32))
+        else:
+            t = timed(lambda: O.mm(a, b, upcast=torch.float32))
+        detail[f"gemm[{name}]"] = t * 64
+    total = sum(detail.values())
+    sample = ("per operator: norm/rope 1024 of 4096 tokens, silu_and_mul 512 of 4096 rows, prefill one 512-token "
+              "sequence (scaled by FLOPs), decode 4 sequences x 2048 context (scaled by context tokens), GEMMs 128 "
+              "of 8192 rows; fp32 torch CPU")
+    return total, len(detail), sample, detail
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    for _ in range(min(args.warmup, 1)):
+        cpu_step_sample()
+    times = []
+    n_ops = 10
+    sample = ""
+    for _ in range(args.steps):
+        t, n_ops, sample, _ = cpu_step_sample()
+        times.append(t)
+    step_s = statistics.mean(times)
+    val = n_ops / step_s
+    out = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out))
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": "operator-path step at configs 2-5: T=4096 hidden=4096 elementwise block; 16-seq varlen causal "
+                    "GQA prefill (32/8 heads, d=128, len 128..4096); batch-256 paged decode (ctx 512..8192, block 16)"
+                    " with cache write; mm/addmm M=8192 at qkv/o/gate_up/down",
+        "ops_per_step": 10,
+        "parallelism": "single GPU" if n_gpus == 1 else
+                       f"{n_gpus} ranks: sequences sharded with no exchange; projections column-parallel + NCCL all-gather",
+        "l2": "no explicit flush: the step cycles through ~8 GB of operands, every operator's inputs are evicted "
+              "from the 126 MB L2 between its consecutive invocations",
+    }
+
+
+# --------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3  # timing rule: at least three warm-up steps
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+
+    from flaggems_b200 import _lib
+
+    peaks, peak_kind = load_peaks()
+    step = Step(device, rank, world)
+    n_ops = len(step.ops)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step.run()
+    barrier()
+
+    events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_ops)]
+              for _ in range(args.steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    time.sleep(0.25)
+    launches0 = _lib.launch_count()
+    barrier()
+    t0 = time.time()
+    e0.record()
+    for s in range(args.steps):
+        step.run(events[s])
+    e1.record()
+    barrier()
+    t1 = time.time()
+    launches = _lib.launch_count() - launches0
+    clocks = sampler.stop(t0, t1)
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * n_ops / (ms_step * 1e-3)
+
+    per_op = []
+    for i, (name, _, work, kind) in enumerate(step.ops):
+        ms = statistics.mean(events[s][i][0].elapsed_time(events[s][i][1]) for s in range(args.steps))
+        if kind == "hbm":
+            ach, peak, unit = work / ms / 1e6, peaks["hbm_gbs"], "GB/s"
+        else:
+            ach, peak, unit = work / ms / 1e9, peaks["bf16_tflops_sustained"], "TFLOP/s"
+        per_op.append({"op": name, "ms": round(ms, 4), "bound": kind, "achieved": round(ach, 1), "unit": unit,
+                       "peak": peak, "frac": round(ach / peak, 3)})
+    dom = max(per_op, key=lambda o: o["ms"])
+    roofline = {"bound": dom["bound"], "kernel": dom["op"], "achieved": dom["achieved"], "peak": dom["peak"],
+                "unit": dom["unit"], "frac": dom["frac"], "peak_source": peak_kind,
+                "traffic": None}
+
+    # ---- end to end: pinned host buffers in and out, copies inside the timed region
+    h2d, d2h = step.make_e2e()
+    for _ in range(2):
+        step.run_e2e()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step.run_e2e()
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_e2e = float(t.item())
+    e2e_val = world * n_ops / (ms_e2e / args.steps * 1e-3)
+    status = _lib.device_status(reset=True)
+
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(world), "roofline": roofline,
+        "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": int(launches), "clocks": clocks, "per_op": per_op, "device_status": status,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        t, n, sample, detail = cpu_step_sample()
+        out["cpu_baseline"] = {"value": n / t, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": sample, "step_seconds_scaled": t}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
