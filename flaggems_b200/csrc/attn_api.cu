@@ -65,6 +65,7 @@ extern "C" int fg_flash_attn_varlen(const fg_attn_params* p, void* stream) {
     FG_REQUIRE(p->block_size > 0 && p->num_blocks > 0, "flash_attn_varlen: paged KV needs block_size and num_blocks");
   } else {
     FG_REQUIRE(p->cu_seqlens_k != nullptr, "cu_seqlens_k or seqused_k must be provided");
+    FG_REQUIRE(p->total_k >= 0, "flash_attn_varlen: negative total_k");
   }
   auto al = [](const void* ptr) { return aligned16(ptr); };
   FG_REQUIRE(al(p->q) && al(p->k) && al(p->v) && al(p->out), "flash_attn_varlen: tensors must be 16-byte aligned");
@@ -89,6 +90,7 @@ extern "C" int fg_flash_attn_varlen(const fg_attn_params* p, void* stream) {
   a.o_rs = p->o_row_stride; a.o_hs = p->o_head_stride;
   a.bt_stride = p->block_table_stride; a.alibi_bs = p->alibi_batch_stride;
   a.total_q = p->total_q;
+  a.total_k = p->total_k;
   a.batch = (int)p->batch; a.H = (int)p->num_heads; a.Hk = (int)p->num_heads_k;
   a.group = a.H / a.Hk; a.D = (int)p->head_dim;
   a.max_q = (int)p->max_seqlen_q; a.max_k = (int)p->max_seqlen_k;

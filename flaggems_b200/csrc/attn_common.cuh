@@ -13,7 +13,7 @@ struct AttnArgs {
   const float* alibi;
   int64_t q_rs, q_hs, k_rs, k_hs, k_bs, v_rs, v_hs, v_bs, o_rs, o_hs;
   int64_t bt_stride, alibi_bs;
-  int64_t total_q;
+  int64_t total_q, total_k;
   int batch, H, Hk, group, D;
   int max_q, max_k, block_size, num_blocks;
   int wl, wr;         // window, -1 = unbounded (wr == 0 when causal)

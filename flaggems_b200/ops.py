@@ -317,6 +317,7 @@ def flash_attn_varlen_func(
     else:
         p.k_row_stride, p.k_head_stride = k.stride(0), k.stride(1)
         p.v_row_stride, p.v_head_stride = v.stride(0), v.stride(1)
+        p.total_k = k.size(0)
     p.alibi_batch_stride = alibi_slopes.stride(0) if (alibi_slopes is not None and alibi_slopes.dim() == 2) else 0
     p.total_q, p.batch, p.num_heads, p.num_heads_k, p.head_dim = total_q, batch_size, num_heads, num_heads_k, head_size
     p.max_seqlen_q, p.max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)

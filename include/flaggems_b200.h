@@ -206,6 +206,7 @@ typedef struct {
   int64_t max_seqlen_q, max_seqlen_k;
   int64_t block_size, num_blocks;
   int64_t window_left, window_right; /* -1 = unbounded */
+  int64_t total_k;                   /* rows of k/v in the contiguous form (0 when paged) */
   double softmax_scale;
   double softcap; /* 0 = off */
   int32_t causal;

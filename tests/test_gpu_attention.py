@@ -89,6 +89,7 @@ def _params_for(q, kc, vc, cu, used, bt, max_q, max_k):
     p.max_seqlen_q, p.max_seqlen_k = max_q, max_k
     p.block_size, p.num_blocks = kc.shape[1], kc.shape[0]
     p.window_left = p.window_right = -1
+    p.softmax_scale = float(q.shape[2]) ** -0.5
     p.causal, p.dtype = 1, _lib.dtype_code(q.dtype)
     return p
 
@@ -223,3 +224,38 @@ def test_decode_config4_reduced_with_cache_write(fg):
     # the last key of each context is the token just written
     last = b.slot_mapping
     assert torch.equal(b.key_cache.view(-1, 8, 128)[last], b.new_key)
+
+
+@pytest.mark.parametrize("block_size", [8, 16, 64, 128, 256])
+@pytest.mark.parametrize("num_heads", [(8, 2), (4, 4), (6, 2)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [True, False])
+def test_prefill_tcgen05_path(fg, block_size, num_heads, dtype, causal):
+    # q_len == k_len, q_len < k_len (chunked prefill) and q_len > k_len (rows without keys),
+    # lengths straddling the 128-row tiles
+    seq_lens = [(300, 300), (128, 129), (65, 700), (200, 90), (257, 1024)]
+    num_blocks = max(64, 4096 // block_size)
+    q, kc, vc, cu, used, bt, qlens, klens = _make(seq_lens, num_heads, 128, block_size, num_blocks, dtype, seed=3)
+    assert _lib.load().fg_flash_attn_path(ctypes.byref(_params_for(q, kc, vc, cu, used, bt, 300, 1024))) == 1
+    # poison the cache rows past each sequence end in its last page: they must not leak
+    out, lse = fg.flash_attn_varlen_func(q, kc, vc, max(qlens), cu, max(klens), seqused_k=used, causal=causal,
+                                         block_table=bt, return_softmax_lse=True)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, 128 ** -0.5, causal=causal)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    assert torch.isfinite(out).all()
+
+
+def test_prefill_tcgen05_ignores_garbage_past_sequence_end(fg):
+    # a cache whose unused slots hold NaN / Inf (torch.empty caches do): results unchanged
+    b = workloads.prefill_batch(seed=21, num_seqs=3, min_len=130, max_len=500, q_heads=8, kv_heads=2, device=DEV)
+    clean = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                      seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+    kc, vc = b.key_cache.clone(), b.value_cache.clone()
+    for i, n in enumerate(b.kv_lens):
+        if n % 16:
+            page = int(b.block_table[i, (n - 1) // 16])
+            kc[page, n % 16:] = float("nan")
+            vc[page, n % 16:] = float("inf")
+    dirty = fg.flash_attn_varlen_func(b.q, kc, vc, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                      seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+    assert torch.equal(clean, dirty)

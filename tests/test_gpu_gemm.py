@@ -63,7 +63,7 @@ def test_addmm(fg, M, N, K, scalar, dtype, b_column_major):
 
 
 TC_SHAPES = [(128, 256, 64), (256, 512, 4096), (1000, 776, 520), (4096, 4096, 4096), (129, 264, 72), (64, 64, 32),
-             (2048, 6144, 4096), (300, 8, 4096), (8, 3000, 128)]
+             (2048, 6144, 4096), (300, 16, 4096), (8, 3000, 128)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)
@@ -74,7 +74,8 @@ def test_mm_tcgen05(fg, M, N, K, dtype, a_col, b_col):
     a = torch.randn((K, M), dtype=dtype, device=DEV).t() if a_col else torch.randn((M, K), dtype=dtype, device=DEV)
     b = torch.randn((N, K), dtype=dtype, device=DEV).t() if b_col else torch.randn((K, N), dtype=dtype, device=DEV)
     res = fg.mm(a, b)
-    assert _uses_tcgen05(a, b, res), "expected the tcgen05 path for this shape"
+    # a column-major A needs a leading dimension that is a multiple of 16 bytes for TMA
+    assert _uses_tcgen05(a, b, res) == (not a_col or M % 8 == 0), "unexpected kernel path for this shape"
     # CPU fp64 oracle on all rows when small, else on a sample that covers tile edges
     if M <= 512:
         rows = torch.arange(M, device=DEV)
