@@ -93,6 +93,8 @@ SIGNATURES = {
     "fg_flash_attn_varlen": (C.c_int, [C.POINTER(AttnParams), _P]),
     "fg_flash_attn_workspace_bytes": (C.c_int64, [_I64] * 5),
     "fg_flash_attn_path": (C.c_int, [C.POINTER(AttnParams)]),
+    "fg_flash_attn_decode_static": (C.c_int, [C.POINTER(AttnParams), _P]),
+    "fg_flash_attn_decode_static_capacity": (C.c_int64, []),
 }
 
 

@@ -222,6 +222,36 @@ FG_API int64_t fg_flash_attn_workspace_bytes(int64_t batch, int64_t num_heads,
  * 1 tcgen05 prefill, 2 split-KV decode.  Pure host logic. */
 FG_API int fg_flash_attn_path(const fg_attn_params* p);
 
+/* ------------------------------------------------------------------------
+ * flash_attn_decode_static: single-token (decode) attention that allocates nothing.
+ * No counterpart in the reference.
+ *
+ * Same arguments and result as fg_flash_attn_varlen for a decode batch (one query
+ * token per sequence, no ALiBi, no window, at most 16 query heads per KV head), but the
+ * scratch for the split-KV partial results is a fixed array inside the library image
+ * (fg_flash_attn_decode_static_capacity() bytes, 64 MiB, resident on every GPU that
+ * loads the library) instead of `workspace`, which is ignored.  It exists for callers
+ * that cannot allocate device memory at call time: runtimes that gave all free memory
+ * to their KV-cache pool at start-up, hosts that bind this ABI without an allocator of
+ * their own, and decode loops that must not hit the device-wide synchronisation of
+ * cudaMalloc/cudaFree.  The call itself performs no cudaMalloc, cudaFree or other
+ * allocating library call.
+ *
+ * Limits and rules:
+ *  - a batch whose chunk plan needs more than the capacity is rejected with
+ *    FG_ERR_TOO_LARGE (need = chunks * batch * num_heads * (head_dim + 1) * 4 bytes, with
+ *    chunks = ceil(max_seqlen_k / chunk) and chunk between 256 and 1024 tokens);
+ *  - the first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current); make that first call before any
+ *    stream capture is started;
+ *  - all calls on a device share the one array, which keeps whatever the last call
+ *    left in it.  Nothing in it has to start at zero (every slot that is read was
+ *    written by the same call), but two calls that may run at the same time on one GPU
+ *    (different streams) would overwrite each other's partial results: serialise them.
+ * ---------------------------------------------------------------------- */
+FG_API int fg_flash_attn_decode_static(const fg_attn_params* p, void* stream);
+FG_API int64_t fg_flash_attn_decode_static_capacity(void);
+
 #ifdef __cplusplus
 }
 #endif
