@@ -326,8 +326,25 @@ void decode_split_plan(int64_t batch, int64_t num_heads_k, int64_t max_seqlen_k,
   *num_splits = (int)((max_seqlen_k + chunk - 1) / chunk);
 }
 
+bool attn_decode_tma_eligible(const AttnArgs& a);
+int attn_decode_tma(const AttnArgs& a, int dtype, int chunk_tokens, cudaStream_t st);
+
+// Combine pass shared by both decode kernels.
+int launch_decode_combine(const AttnArgs& a, int dtype, cudaStream_t st) {
+  dim3 cgrid((unsigned)a.total_q, a.H);
+  if (dtype == FG_BF16)
+    attn_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, st>>>(a);
+  else
+    attn_combine_kernel<__half><<<cgrid, 128, 0, st>>>(a);
+  FG_CHECK_LAUNCH("attn_combine_kernel");
+  return FG_OK;
+}
+
 int attn_decode(const AttnArgs& a, int dtype, int chunk_tokens, cudaStream_t st) {
   if (a.batch > 65535 || a.Hk > 65535) return fail(FG_ERR_TOO_LARGE, "flash_attn: batch or heads above 65535");
+  // TMA-fed kernel whenever the cache geometry allows one box per page; the cp.async
+  // kernel below covers the remaining block sizes.
+  if (attn_decode_tma_eligible(a)) return attn_decode_tma(a, dtype, chunk_tokens, st);
   if (dtype == FG_BF16) {
     if (a.D <= 64) return launch_decode<__nv_bfloat16, 64, 3>(a, chunk_tokens, st);
     if (a.D <= 128) return launch_decode<__nv_bfloat16, 128, 3>(a, chunk_tokens, st);

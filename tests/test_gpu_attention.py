@@ -259,3 +259,43 @@ def test_prefill_tcgen05_ignores_garbage_past_sequence_end(fg):
     dirty = fg.flash_attn_varlen_func(b.q, kc, vc, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
                                       seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
     assert torch.equal(clean, dirty)
+
+
+@pytest.mark.parametrize("block_size", [8, 16, 24, 48, 64, 128, 256])
+@pytest.mark.parametrize("head_size", [64, 96, 128, 192])
+def test_decode_block_sizes_and_head_dims(fg, block_size, head_size):
+    # power-of-two pages take the TMA-fed kernel, the others the cp.async kernel; head dims
+    # that are not multiples of 64 rely on TMA zero fill of the last 64-column box
+    seq_lens = [(1, 700), (1, 64), (1, 3), (1, 1025)]
+    q, kc, vc, cu, used, bt, qlens, klens = _make(seq_lens, (8, 2), head_size, block_size, 300, torch.bfloat16, seed=5)
+    out = fg.flash_attn_varlen_func(q, kc, vc, 1, cu, 1025, seqused_k=used, causal=True, block_table=bt)
+    ref = _oracle(q, kc, vc, qlens, klens, bt, head_size ** -0.5)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+
+
+def test_decode_contiguous_kv_and_garbage_tail(fg):
+    # packed K/V with cu_seqlens_k (no page table), one query token per sequence
+    torch.manual_seed(9)
+    klens = [300, 17, 1000]
+    cu_k = torch.tensor([0] + klens, dtype=torch.int32).cumsum(0, dtype=torch.int32).to(DEV)
+    cu_q = torch.arange(4, dtype=torch.int32, device=DEV)
+    q = torch.randn(3, 8, 128, dtype=torch.float16, device=DEV)
+    k = torch.randn(sum(klens), 2, 128, dtype=torch.float16, device=DEV)
+    v = torch.randn_like(k)
+    out = fg.flash_attn_varlen_func(q, k, v, 1, cu_q, 1000, cu_seqlens_k=cu_k, causal=True)
+    ref = O.varlen_attention(q.cpu(), k.cpu(), v.cpu(), cu_q.cpu(), cu_k.cpu(), 128 ** -0.5, causal=False,
+                             compute_dtype=torch.float32)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+    # paged: NaN/Inf in the unused tail of the last page must not leak
+    b = workloads.decode_batch(seed=6, batch=6, min_ctx=20, max_ctx=900, device=DEV)
+    clean = fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, 1, b.cu_seqlens_q, b.max_seqlen_k,
+                                      seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+    kc, vc = b.key_cache.clone(), b.value_cache.clone()
+    for i, n in enumerate(b.kv_lens):
+        if n % 16:
+            page = int(b.block_table[i, (n - 1) // 16])
+            kc[page, n % 16:] = float("nan")
+            vc[page, n % 16:] = float("inf")
+    dirty = fg.flash_attn_varlen_func(b.q, kc, vc, 1, b.cu_seqlens_q, b.max_seqlen_k, seqused_k=b.seqused_k,
+                                      causal=True, block_table=b.block_table)
+    assert torch.equal(clean, dirty)
