@@ -75,6 +75,74 @@ struct Cvt<__nv_bfloat16> {
   static __device__ __forceinline__ __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
 };
 
+// Pair conversions on packed 32-bit words (two 16-bit values, or one float in .x).
+// They cost one integer op per element on the way in and one cvt per pair on the way
+// out, half of what element-wise conversion takes -- the memory-bound kernels are
+// close to instruction-issue bound without them.
+template <typename T>
+struct Pair;
+template <>
+struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <>
+struct Pair<__half> {
+  static __device__ __forceinline__ float2 unpack(uint32_t u) {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+// 16 bytes of T as fp32 values and back (4 floats, or 8 halves through Pair<T>).
+template <typename T>
+struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[N]) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 p = Pair<T>::unpack(w[i]);
+      f[2 * i] = p.x;
+      f[2 * i + 1] = p.y;
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[N]) {
+    return make_uint4(Pair<T>::pack(f[0], f[1]), Pair<T>::pack(f[2], f[3]), Pair<T>::pack(f[4], f[5]),
+                      Pair<T>::pack(f[6], f[7]));
+  }
+};
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[4]) {
+    f[0] = __uint_as_float(u.x);
+    f[1] = __uint_as_float(u.y);
+    f[2] = __uint_as_float(u.z);
+    f[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[4]) {
+    return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+  }
+};
+__device__ __forceinline__ uint4 ldg16_stream(const void* p) {
+  uint4 u;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w)
+               : "l"(p));
+  return u;
+}
+__device__ __forceinline__ uint4 ldg16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void stg16(void* p, const uint4& u) { *reinterpret_cast<uint4*>(p) = u; }
+
 // A 16-byte packet of T (4 floats or 8 halves).
 template <typename T>
 struct alignas(16) Pack16 {

@@ -16,30 +16,29 @@ struct CacheArgs {
   int64_t cbs, crs, chs;   // cache block / row / head strides (elements)
 };
 
-// One packet = 16 bytes inside one head row (D*ES is a multiple of 16).
+// One packet = 16 bytes inside one head row (D*ES is a multiple of 16).  Index math is
+// 32-bit (the host checks that token*packets and the slot range fit).
 template <int ES>
-__global__ void __launch_bounds__(256) cache_scatter_vec_kernel(CacheArgs a, int packs_per_head) {
-  const int64_t packs_per_tok = a.H * packs_per_head;
-  const int64_t total = a.T * packs_per_tok * 2;
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t tk = idx / packs_per_tok;  // token * 2 + which
-    const int64_t r = idx - tk * packs_per_tok;
-    const int64_t tok = tk >> 1;
-    const int which = (int)(tk & 1);
-    const int64_t slot = a.slots[tok];
-    if (slot < 0 || slot >= a.NB * a.BS) continue;  // padding, or outside the cache
-    const int64_t h = r / packs_per_head;
-    const int64_t c = r - h * packs_per_head;
-    const int64_t blk = slot / a.BS, off = slot - blk * a.BS;
-    const char* src = (which ? a.value + tok * a.vs * ES : a.key + tok * a.ks * ES) +
-                      (h * a.D) * ES + c * 16;
-    char* dst = (which ? a.vc : a.kc) + (blk * a.cbs + off * a.crs + h * a.chs) * ES + c * 16;
-    uint4 v;
-    asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(src));
-    *reinterpret_cast<uint4*>(dst) = v;
+__global__ void __launch_bounds__(256) cache_scatter_vec_kernel(CacheArgs a, uint32_t packs_per_head,
+                                                                uint32_t packs_per_tok, uint32_t total,
+                                                                uint32_t num_slots) {
+  for (uint32_t idx = blockIdx.x * 256u + threadIdx.x; idx < total; idx += gridDim.x * 256u) {
+    const uint32_t tk = idx / packs_per_tok;  // token * 2 + which
+    const uint32_t r = idx - tk * packs_per_tok;
+    const uint32_t tok = tk >> 1;
+    const bool which = tk & 1;
+    const uint32_t h = r / packs_per_head;
+    const uint32_t c = r - h * packs_per_head;
+    const char* src = (which ? a.value + (int64_t)tok * a.vs * ES : a.key + (int64_t)tok * a.ks * ES) +
+                      ((int64_t)h * a.D) * ES + c * 16;
+    // the payload does not depend on the slot: fetch both in the same round trip
+    const uint4 payload = ldg16_stream(src);
+    const int64_t slot64 = a.slots[tok];
+    if (slot64 < 0 || slot64 >= (int64_t)num_slots) continue;  // padding, or outside the cache
+    const uint32_t slot = (uint32_t)slot64;
+    const uint32_t blk = slot / (uint32_t)a.BS, off = slot - blk * (uint32_t)a.BS;
+    char* dst = (which ? a.vc : a.kc) + ((int64_t)blk * a.cbs + (int64_t)off * a.crs + (int64_t)h * a.chs) * ES + c * 16;
+    stg16(dst, payload);
   }
 }
 
@@ -92,16 +91,18 @@ extern "C" int fg_reshape_and_cache_flash(const void* key, const void* value, vo
   const bool vec = b16(head_size) && b16(key_stride) && b16(value_stride) && b16(cache_block_stride) &&
                    b16(cache_row_stride) && b16(cache_head_stride) && aligned16(key) &&
                    aligned16(value) && aligned16(key_cache) && aligned16(value_cache);
-  const int64_t cap = (int64_t)num_sms() * 16;
-  if (vec) {
-    const int pph = (int)(head_size * es / 16);
-    const int64_t total = num_tokens * num_heads * pph * 2;
-    int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)num_sms() * 32;
+  const int64_t vtotal = num_tokens * num_heads * (head_size * es / 16) * 2;
+  if (vec && vtotal < 4000000000LL && num_blocks * block_size < 4000000000LL) {
+    const uint32_t pph = (uint32_t)(head_size * es / 16);
+    const uint32_t ppt = (uint32_t)num_heads * pph;
+    int64_t blocks = (vtotal + 255) / 256;
     if (blocks > cap) blocks = cap;
+    const uint32_t nslots = (uint32_t)(num_blocks * block_size);
     switch (es) {
-      case 1: cache_scatter_vec_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(a, pph); break;
-      case 2: cache_scatter_vec_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(a, pph); break;
-      default: cache_scatter_vec_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(a, pph); break;
+      case 1: cache_scatter_vec_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(a, pph, ppt, (uint32_t)vtotal, nslots); break;
+      case 2: cache_scatter_vec_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(a, pph, ppt, (uint32_t)vtotal, nslots); break;
+      default: cache_scatter_vec_kernel<4><<<(unsigned)blocks, 256, 0, st>>>(a, pph, ppt, (uint32_t)vtotal, nslots); break;
     }
     FG_CHECK_LAUNCH("cache_scatter_vec_kernel");
   } else {

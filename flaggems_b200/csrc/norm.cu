@@ -18,13 +18,14 @@ __device__ __forceinline__ float block_sum(float v, float* smem) {
   return t;  // every thread of every warp holds the total
 }
 
-// Row held in registers: thread t owns packs t, t+blockDim, ... (VPT of them).
+// Row held in registers: thread t owns packets t, t+blockDim, ... (VPT of them).  All
+// loads of the row are issued before the first use; conversions work on packed pairs.
 template <typename T, int VPT, bool HAS_RES>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(VPT >= 8 ? 512 : 1024)
 rms_norm_row_kernel(T* x, T* res, const T* __restrict__ w,
                     T* out, int64_t N, int64_t x_stride, int64_t r_stride,
                     int64_t o_stride, float eps) {
-  constexpr int E = Pack16<T>::N;
+  constexpr int E = Vec16<T>::N;
   __shared__ float red[32];
   const int64_t row = blockIdx.x;
   T* xr = x + row * x_stride;
@@ -32,25 +33,29 @@ rms_norm_row_kernel(T* x, T* res, const T* __restrict__ w,
   T* orow = out + row * o_stride;
   const int npacks = (int)(N / E);
 
+  uint4 xa[VPT], ra[VPT], wa[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int p = threadIdx.x + i * blockDim.x;
+    if (p < npacks) {
+      xa[i] = ldg16_stream(xr + (int64_t)p * E);
+      if (HAS_RES) ra[i] = ldg16_stream(rr + (int64_t)p * E);
+      wa[i] = ldg16(w + (int64_t)p * E);  // issued with the row so that it is not a second round trip
+    }
+  }
   float s[VPT][E];
   float sumsq = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int p = threadIdx.x + i * blockDim.x;
     if (p < npacks) {
-      Pack16<T> a = ld16_stream(xr + (int64_t)p * E);
+      Vec16<T>::unpack(xa[i], s[i]);
       if (HAS_RES) {
-        Pack16<T> b = ld16_stream(rr + (int64_t)p * E);
-        Pack16<T> o;
+        float rv[E];
+        Vec16<T>::unpack(ra[i], rv);
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          s[i][e] = Cvt<T>::to_f32(a.v[e]) + Cvt<T>::to_f32(b.v[e]);
-          o.v[e] = Cvt<T>::from_f32(s[i][e]);
-        }
-        st16(rr + (int64_t)p * E, o);
-      } else {
-#pragma unroll
-        for (int e = 0; e < E; ++e) s[i][e] = Cvt<T>::to_f32(a.v[e]);
+        for (int e = 0; e < E; ++e) s[i][e] += rv[e];
+        stg16(rr + (int64_t)p * E, Vec16<T>::pack(s[i]));  // residual: the sum rounded to T
       }
 #pragma unroll
       for (int e = 0; e < E; ++e) sumsq = fmaf(s[i][e], s[i][e], sumsq);
@@ -62,12 +67,11 @@ rms_norm_row_kernel(T* x, T* res, const T* __restrict__ w,
   for (int i = 0; i < VPT; ++i) {
     const int p = threadIdx.x + i * blockDim.x;
     if (p < npacks) {
-      Pack16<T> ww = ld16(w + (int64_t)p * E);
-      Pack16<T> o;
+      float wv[E];
+      Vec16<T>::unpack(wa[i], wv);
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        o.v[e] = Cvt<T>::from_f32(s[i][e] * rrms * Cvt<T>::to_f32(ww.v[e]));
-      st16(orow + (int64_t)p * E, o);
+      for (int e = 0; e < E; ++e) s[i][e] = s[i][e] * rrms * wv[e];
+      stg16(orow + (int64_t)p * E, Vec16<T>::pack(s[i]));
     }
   }
 }

@@ -36,17 +36,39 @@ __device__ __forceinline__ int64_t rope_position(const RopeArgs& a, int64_t tok)
   return pos;
 }
 
-// Vector kernel: unit stride over D, 16-byte aligned rows, (D/2) % E == 0 for NeoX
-// or D % E == 0 for interleaved.
-template <typename T, typename CT, bool INTERLEAVED>
+// N consecutive cos (or sin) values as fp32.  VEC: the row is 16-byte aligned and N
+// values are a whole number of 16-byte packets.
+template <typename CT, int N, bool VEC>
+__device__ __forceinline__ void load_table(const CT* p, float (&f)[N]) {
+  if constexpr (VEC) {
+    constexpr int PE = Vec16<CT>::N;
+#pragma unroll
+    for (int i = 0; i < N / PE; ++i) {
+      float t[PE];
+      Vec16<CT>::unpack(ldg16(p + i * PE), t);
+#pragma unroll
+      for (int e = 0; e < PE; ++e) f[i * PE + e] = t[e];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = Cvt<CT>::to_f32(p[i]);
+  }
+}
+
+// Vector kernel: unit stride over D, 16-byte aligned rows.  One work item covers E
+// rotation pairs: NeoX -> the packets at j0 and j0 + D/2; interleaved -> two adjacent
+// packets.  Needs (D/2) % E == 0.  One CTA per token, one item per thread; the kernel is
+// kept lean in registers (packed words are converted pair by pair) because the bytes in
+// flight per SM are set by how many of these small CTAs are resident.
+template <typename T, typename CT, bool INTERLEAVED, bool CSVEC>
 __global__ void __launch_bounds__(512) rope_vec_kernel(RopeArgs a) {
-  constexpr int E = Pack16<T>::N;
+  constexpr int E = Vec16<T>::N;
   const int64_t tok = blockIdx.x;
   const int64_t pos = rope_position(a, tok);
   const CT* cosr = reinterpret_cast<const CT*>(a.cos) + pos * a.cos_stride;
   const CT* sinr = reinterpret_cast<const CT*>(a.sin) + pos * a.sin_stride;
   const int half = a.D >> 1;
-  const int cph = INTERLEAVED ? a.D / E : half / E;  // chunks per head
+  const int cph = half / E;  // work items per head
   const int work = (a.Hq + a.Hk) * cph;
   for (int w = threadIdx.x; w < work; w += blockDim.x) {
     const int h = w / cph;
@@ -56,38 +78,39 @@ __global__ void __launch_bounds__(512) rope_vec_kernel(RopeArgs a) {
                         : reinterpret_cast<const T*>(a.k) + tok * a.ks_t + (int64_t)(h - a.Hq) * a.ks_h;
     T* dst = is_q ? reinterpret_cast<T*>(a.qo) + tok * a.qos_t + (int64_t)h * a.qos_h
                   : reinterpret_cast<T*>(a.ko) + tok * a.kos_t + (int64_t)(h - a.Hq) * a.kos_h;
+    const int j0 = c * E;                               // first rotation pair of this item
+    const int o0 = INTERLEAVED ? 2 * j0 : j0;           // element offsets of the two packets
+    const int o1 = INTERLEAVED ? 2 * j0 + E : j0 + half;
+    const uint4 u0 = ldg16(src + o0);
+    const uint4 u1 = ldg16(src + o1);
+    float cs[E], sn[E];
+    load_table<CT, E, CSVEC>(cosr + j0, cs);
+    load_table<CT, E, CSVEC>(sinr + j0, sn);
+    float x[E], y[E];
+    Vec16<T>::unpack(u0, x);
+    Vec16<T>::unpack(u1, y);
     if (!INTERLEAVED) {
-      const int j0 = c * E;
-      Pack16<T> lo = ld16(src + j0);
-      Pack16<T> hi = ld16(src + j0 + half);
-      Pack16<T> olo, ohi;
 #pragma unroll
       for (int e = 0; e < E; ++e) {
-        const float cs = Cvt<CT>::to_f32(cosr[j0 + e]);
-        const float sn = Cvt<CT>::to_f32(sinr[j0 + e]);
-        const float x0 = Cvt<T>::to_f32(lo.v[e]);
-        const float x1 = Cvt<T>::to_f32(hi.v[e]);
-        olo.v[e] = Cvt<T>::from_f32(x0 * cs - x1 * sn);
-        ohi.v[e] = Cvt<T>::from_f32(x1 * cs + x0 * sn);
+        const float r0 = x[e] * cs[e] - y[e] * sn[e];
+        y[e] = y[e] * cs[e] + x[e] * sn[e];
+        x[e] = r0;
       }
-      st16(dst + j0, olo);
-      st16(dst + j0 + half, ohi);
     } else {
-      const int i0 = c * E;
-      Pack16<T> x = ld16(src + i0);
-      Pack16<T> o;
+      // packet 0 holds pairs j0 .. j0+E/2-1 as (even, odd) neighbours, packet 1 the rest
 #pragma unroll
       for (int e = 0; e < E; e += 2) {
-        const int j = (i0 + e) >> 1;
-        const float cs = Cvt<CT>::to_f32(cosr[j]);
-        const float sn = Cvt<CT>::to_f32(sinr[j]);
-        const float x0 = Cvt<T>::to_f32(x.v[e]);
-        const float x1 = Cvt<T>::to_f32(x.v[e + 1]);
-        o.v[e] = Cvt<T>::from_f32(x0 * cs - x1 * sn);
-        o.v[e + 1] = Cvt<T>::from_f32(x1 * cs + x0 * sn);
+        const int j = e >> 1, k = E / 2 + j;
+        const float a0 = x[e] * cs[j] - x[e + 1] * sn[j];
+        x[e + 1] = x[e + 1] * cs[j] + x[e] * sn[j];
+        x[e] = a0;
+        const float b0 = y[e] * cs[k] - y[e + 1] * sn[k];
+        y[e + 1] = y[e + 1] * cs[k] + y[e] * sn[k];
+        y[e] = b0;
       }
-      st16(dst + i0, o);
     }
+    stg16(dst + o0, Vec16<T>::pack(x));
+    stg16(dst + o1, Vec16<T>::pack(y));
   }
 }
 
@@ -146,17 +169,24 @@ static int launch_rope(const fg_rope_params* p, cudaStream_t st) {
   if (a.Hk > 0)
     vec = vec && aligned16(a.k) && aligned16(a.ko) && mult(a.ks_t) && mult(a.ks_h) &&
           mult(a.kos_t) && mult(a.kos_h);
-  vec = vec && (p->interleaved ? (a.D % E == 0) : (half % E == 0));
+  vec = vec && (half % E == 0);
+  // cos/sin rows readable as 16-byte packets?
+  constexpr int CE = 16 / (int)sizeof(CT);
+  const bool csvec = aligned16(a.cos) && aligned16(a.sin) && a.cos_stride % CE == 0 && a.sin_stride % CE == 0 &&
+                     (E % CE == 0);
   dim3 grid((unsigned)a.T);
   if (vec) {
-    const int cph = p->interleaved ? a.D / E : half / E;
+    const int cph = half / E;
     int threads = (a.Hq + a.Hk) * cph;
     threads = (threads + 31) / 32 * 32;
     if (threads > 512) threads = 512;
-    if (p->interleaved)
-      rope_vec_kernel<T, CT, true><<<grid, threads, 0, st>>>(a);
-    else
-      rope_vec_kernel<T, CT, false><<<grid, threads, 0, st>>>(a);
+    if (p->interleaved) {
+      if (csvec) rope_vec_kernel<T, CT, true, true><<<grid, threads, 0, st>>>(a);
+      else rope_vec_kernel<T, CT, true, false><<<grid, threads, 0, st>>>(a);
+    } else {
+      if (csvec) rope_vec_kernel<T, CT, false, true><<<grid, threads, 0, st>>>(a);
+      else rope_vec_kernel<T, CT, false, false><<<grid, threads, 0, st>>>(a);
+    }
     FG_CHECK_LAUNCH("rope_vec_kernel");
   } else {
     int threads = (a.Hq + a.Hk) * half;

@@ -9,37 +9,52 @@ namespace fg {
 __device__ __forceinline__ float silu_mul_f32(float x, float y) {
   return x / (1.0f + __expf(-x)) * y;
 }
+// 16-bit outputs carry 8-11 significant bits: ex2.approx + rcp.approx (about 2 ulp in
+// fp32) are exact enough and keep the kernel off the instruction-issue limit.
+__device__ __forceinline__ float silu_mul_fast(float x, float y) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return x * r * y;
+}
+template <typename T>
+__device__ __forceinline__ float silu_mul_t(float x, float y) {
+  return sizeof(T) == 4 ? silu_mul_f32(x, y) : silu_mul_fast(x, y);
+}
 
-template <typename T, int UNROLL>
+// [rows, cols] view; IDX is uint32_t when the packet count allows it (one 32-bit
+// division per packet instead of a 64-bit one).
+template <typename T, int UNROLL, typename IDX>
 __global__ void __launch_bounds__(256)
 silu_mul_rows_kernel(const T* a, const T* b, T* out,
                      int64_t total_packs, int packs_per_row, int64_t a_stride, int64_t b_stride,
                      int64_t o_stride) {
-  constexpr int E = Pack16<T>::N;
-  const int64_t base = ((int64_t)blockIdx.x * UNROLL) * blockDim.x + threadIdx.x;
-  Pack16<T> pa[UNROLL], pb[UNROLL];
+  constexpr int E = Vec16<T>::N;
+  const IDX base = (IDX)blockIdx.x * (IDX)(UNROLL * 256) + threadIdx.x;
+  uint4 pa[UNROLL], pb[UNROLL];
   int64_t ooff[UNROLL];
   bool ok[UNROLL];
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
-    const int64_t idx = base + (int64_t)u * blockDim.x;
-    ok[u] = idx < total_packs;
+    const IDX idx = base + (IDX)(u * 256);
+    ok[u] = (int64_t)idx < total_packs;
     if (ok[u]) {
-      const int64_t row = idx / packs_per_row;
-      const int64_t col = (idx - row * packs_per_row) * E;
-      pa[u] = ld16_stream(a + row * a_stride + col);
-      pb[u] = ld16_stream(b + row * b_stride + col);
-      ooff[u] = row * o_stride + col;
+      const IDX row = idx / (IDX)packs_per_row;
+      const int64_t col = (int64_t)(idx - row * (IDX)packs_per_row) * E;
+      pa[u] = ldg16_stream(a + (int64_t)row * a_stride + col);
+      pb[u] = ldg16_stream(b + (int64_t)row * b_stride + col);
+      ooff[u] = (int64_t)row * o_stride + col;
     }
   }
 #pragma unroll
   for (int u = 0; u < UNROLL; ++u) {
     if (ok[u]) {
-      Pack16<T> o;
+      float fa[E], fb[E];
+      Vec16<T>::unpack(pa[u], fa);
+      Vec16<T>::unpack(pb[u], fb);
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        o.v[e] = Cvt<T>::from_f32(silu_mul_f32(Cvt<T>::to_f32(pa[u].v[e]), Cvt<T>::to_f32(pb[u].v[e])));
-      st16(out + ooff[u], o);
+      for (int e = 0; e < E; ++e) fa[e] = silu_mul_t<T>(fa[e], fb[e]);
+      stg16(out + ooff[u], Vec16<T>::pack(fa));
     }
   }
 }
@@ -104,12 +119,16 @@ static int launch_silu_mul(const T* a, const T* b, T* out, int ndim, const int64
               (ras % E == 0) && (rbs % E == 0) && (ros % E == 0);
   }
   if (rows_ok && cols / E <= 2147483647LL) {
-    constexpr int UNROLL = 2;
+    constexpr int UNROLL = 4;
     const int64_t total_packs = total / E;
     const int64_t blocks = (total_packs + 256 * UNROLL - 1) / (256 * UNROLL);
     if (blocks > 2147483647LL) return fail(FG_ERR_TOO_LARGE, "silu_and_mul: tensor too large");
-    silu_mul_rows_kernel<T, UNROLL><<<(unsigned)blocks, 256, 0, st>>>(
-        a, b, out, total_packs, (int)(cols / E), ras, rbs, ros);
+    if (total_packs + 256 * UNROLL < 4294967295LL)
+      silu_mul_rows_kernel<T, UNROLL, uint32_t><<<(unsigned)blocks, 256, 0, st>>>(
+          a, b, out, total_packs, (int)(cols / E), ras, rbs, ros);
+    else
+      silu_mul_rows_kernel<T, UNROLL, int64_t><<<(unsigned)blocks, 256, 0, st>>>(
+          a, b, out, total_packs, (int)(cols / E), ras, rbs, ros);
     FG_CHECK_LAUNCH("silu_mul_rows_kernel");
     return FG_OK;
   }
