@@ -117,28 +117,33 @@ class ClockSampler:
 class Step:
     """The operators of one step with their inputs resident on ``device``."""
 
-    def __init__(self, device, rank: int, world: int, seed: int = 0):
+    def __init__(self, device, rank: int, world: int, seed: int = 0, small: bool = False, only: str = ""):
         import flaggems_b200 as fg
         from flaggems_b200 import workloads as W
 
         self.fg, self.W = fg, W
         self.device, self.rank, self.world = device, rank, world
+        self.only = only
         s = seed + 1000 * rank  # every rank owns a different batch of sequences
         self.x, self.res, self.w, self.eps = W.norm_inputs(seed=s + 1, device=device)
         self.q, self.k, self.cos, self.sin, self.pos = W.rope_inputs(seed=s + 2, device=device)
         self.act = W.silu_inputs(seed=s + 3, device=device)
         self.half = self.act.shape[1] // 2
         self.silu_out = torch.empty((self.act.shape[0], self.half), dtype=self.act.dtype, device=device)
-        self.pre = W.prefill_batch(seed=s + 4, device=device)
+        # --small: reduced attention/GEMM sizes for profiler captures (operands still exceed L2)
+        pre_kw = dict(num_seqs=8, min_len=1024, max_len=3072) if small else {}
+        dec_kw = dict(batch=64, min_ctx=1024, max_ctx=4096) if small else {}
+        self.pre = W.prefill_batch(seed=s + 4, device=device, **pre_kw)
         self.pre_out = torch.empty_like(self.pre.q)
-        self.dec = W.decode_batch(seed=s + 5, device=device)
+        self.dec = W.decode_batch(seed=s + 5, device=device, **dec_kw)
         self.dec_out = torch.empty_like(self.dec.q)
         # projections: A replicated (same seed on every rank), B/bias = this rank's column shard
         self.gemm = {}
         for i, name in enumerate(W.GEMM_SHAPES):
-            a, b, bias = W.gemm_inputs(name, seed=seed + 10 + i, device=device)
+            a, b, bias = W.gemm_inputs(name, seed=seed + 10 + i, device=device, M=2048 if small else 8192)
             if world > 1:  # the shard of a [K, N * world] weight owned by this rank
-                _, b, bias = W.gemm_inputs(name, seed=seed + 10 + i + 100 * (rank + 1), device=device)
+                _, b, bias = W.gemm_inputs(name, seed=seed + 10 + i + 100 * (rank + 1), device=device,
+                                           M=2048 if small else 8192)
             c = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=device)
             gathered = None
             if world > 1:
@@ -186,6 +191,10 @@ class Step:
                 ops.append((f"addmm[{name}]", self._gemm_call(name, True), M * N * (2 * K + 1), "tensor"))
             else:
                 ops.append((f"mm[{name}]", self._gemm_call(name, False), 2 * M * N * K, "tensor"))
+        if self.only:
+            ops = [o for o in ops if self.only in o[0]]
+            if not ops:
+                raise SystemExit(f"--only {self.only!r} matches no operator")
         return ops
 
     def _gemm_call(self, name, with_bias):
@@ -325,7 +334,15 @@ def run_reference_arm(args, rank):
     print(json.dumps(out))
 
 
-def workload_config(n_gpus):
+def workload_config(n_gpus, n_ops=10, small=False, only=""):
+    cfg = _workload_config(n_gpus)
+    cfg["ops_per_step"] = n_ops
+    if small or only:
+        cfg["workload"] = f"PROFILING SUBSET (small={small}, only={only!r}) of: " + cfg["workload"]
+    return cfg
+
+
+def _workload_config(n_gpus):
     return {
         "workload": "operator-path step at configs 2-5: T=4096 hidden=4096 elementwise block; 16-seq varlen causal "
                     "GQA prefill (32/8 heads, d=128, len 128..4096); batch-256 paged decode (ctx 512..8192, block 16)"
@@ -346,6 +363,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (PCIe) leg")
+    ap.add_argument("--only", default="", help="run only the operators whose name contains this string")
+    ap.add_argument("--small", action="store_true",
+                    help="reduced attention / GEMM sizes (for profiler captures); not a benchmark configuration")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3  # timing rule: at least three warm-up steps
@@ -368,7 +389,7 @@ def main():
     from flaggems_b200 import _lib
 
     peaks, peak_kind = load_peaks()
-    step = Step(device, rank, world)
+    step = Step(device, rank, world, small=args.small, only=args.only)
     n_ops = len(step.ops)
 
     def barrier():
@@ -420,27 +441,31 @@ def main():
                 "traffic": None}
 
     # ---- end to end: pinned host buffers in and out, copies inside the timed region
-    h2d, d2h = step.make_e2e()
-    for _ in range(2):
-        step.run_e2e()
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        step.run_e2e()
-    e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms_e2e], device=device)
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms_e2e = float(t.item())
-    e2e_val = world * n_ops / (ms_e2e / args.steps * 1e-3)
+    h2d = d2h = 0
+    ms_e2e = float("nan")
+    e2e_val = None
+    if not args.no_e2e:
+        h2d, d2h = step.make_e2e()
+        for _ in range(2):
+            step.run_e2e()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step.run_e2e()
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms_e2e], device=device)
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            ms_e2e = float(t.item())
+        e2e_val = world * n_ops / (ms_e2e / args.steps * 1e-3)
     status = _lib.device_status(reset=True)
 
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": workload_config(world), "roofline": roofline,
+        "data": "synthetic", "config": workload_config(world, n_ops, args.small, args.only), "roofline": roofline,
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clocks, "per_op": per_op, "device_status": status,

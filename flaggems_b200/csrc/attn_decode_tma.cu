@@ -54,6 +54,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const SeqInfo s = seq_info(a, b);
   if (s.q_len < 1) return;
+  // drain after a timed-out wait on this device (one thread reads: CTA-uniform decision)
+  __shared__ int s_drain;
+  if (threadIdx.x == 0) s_drain = *reinterpret_cast<volatile int*>(a.status);
+  __syncthreads();
+  if (s_drain != 0) return;
   const int kv_begin = split * da.chunk_tokens;
   const int kv_end = min(s.k_len, kv_begin + da.chunk_tokens);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;

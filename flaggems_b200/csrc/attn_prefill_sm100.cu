@@ -2,27 +2,46 @@
 //
 // One CTA = 128 query positions of one sequence x TWO query heads of the same KV
 // group (one when the group size is odd): the two 128-row Q tiles share every K/V
-// tile, which halves the K/V traffic and lets the tensor core work on one tile while
-// the softmax warps work on the other (ping-pong).
+// tile, which halves the K/V traffic and lets the tensor pipe work on one tile while
+// the softmax warps work on the other.
 //
 //   warp 0       TMA producer: Q tiles once, then K and V tiles (128 keys x 128) through
 //                two 2-stage rings; paged caches are fetched page by page with one
-//                4-D box per page and half, so a tile lands as a dense K-major tile
-//   warp 1       issues tcgen05.mma: S_t = Q_t K^T (SS, 8 x K16) into TMEM, and
-//                O_t += P_t V (TS: P read from TMEM as the A operand, V as an MN-major
-//                B operand) -- all from one elected thread
-//   warps 4-7    softmax of tile 0: one thread per row (TMEM lane = row): tcgen05.ld the
-//   warps 8-11   row of S, scale, mask, exp2, pack P to 16 bit and tcgen05.st it over
-//   (tile 1)     the S columns; the running max is only raised when it grows by more than
-//                8 (log2 units), so the O accumulator in TMEM is rescaled rarely; the same
-//                warps write the normalised output at the end
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases S_t.
+//                4-D box per page and 64-column half, so a tile lands as a dense,
+//                128-byte-swizzled K-major tile
+//   warp 1       issues tcgen05.mma from one thread: S_t = Q_t K^T as one SS group per 128
+//                keys (M128 N128, 8 x K16 -- an SS instruction costs ~115 cycles whatever
+//                its N, so N is kept at 128), and O_t += P_t V as TS MMAs (P read from TMEM
+//                as the A operand, full rate) in two halves of 64 keys
+//   warps 4-7    softmax of Q tile 0: one thread per row (TMEM lane = row), in two halves of
+//   warps 8-11   64 keys: tcgen05.ld the scores, scale, mask, exp2, pack P to 16 bit and
+//   (tile 1)     tcgen05.st it over the first 32 columns of that half; PV of the first half
+//                runs while the second half is exponentiated.  The running max is only
+//                raised when it grows by more than 8 (log2 units), so the O accumulator in
+//                TMEM is rescaled rarely; the same warps write the normalised output
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P halves alias S halves.
 //
 // Covers: fp16/bf16, head dim 128, causal or full attention, paged (block size a
 // power of two >= 8) or contiguous KV.  ALiBi, soft-cap, windows and other head dims
 // take the general kernel.
 #include "attn_common.cuh"
 #include "sm100_common.cuh"
+
+#ifdef FG_PREFILL_TRACE
+// Debug build only: cycle stamps of one CTA's roles (never part of the shipped library).
+__device__ long long g_fg_trace[8192];
+#define FG_TRACE(slot, idx)                                                   \
+  do {                                                                        \
+    if (trace_on && (idx) < 64) g_fg_trace[(slot) * 64 + (idx)] = clock64(); \
+  } while (0)
+extern "C" __attribute__((visibility("default"))) int fg_debug_read_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_fg_trace, sizeof(long long) * n);
+}
+#else
+#define FG_TRACE(slot, idx) \
+  do {                      \
+  } while (0)
+#endif
 
 namespace fg {
 
@@ -51,6 +70,30 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x on the FMA pipe (the MUFU unit, 4 lanes per clock and scheduler, is what the two
+// softmax warpgroups contend for): split x = n + f with a round-down add, evaluate a
+// cubic for 2^f on [0,1) and add n to the exponent field.  Relative error about 1e-4,
+// far below the 16-bit rounding of P.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float magic = 12582912.0f;                 // 1.5 * 2^23
+  const float xr = __fadd_rd(x, magic);            // integer part in the low mantissa bits
+  const float f = x - (xr - magic);                // [0, 1)
+  float p = fmaf(f, 0.077119873f, 0.227564394f);
+  p = fmaf(p, f, 0.695146143f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + ((__float_as_int(xr) - 0x4B400000) << 23));
+}
+#ifndef FG_PREFILL_POLY_EVERY
+#define FG_PREFILL_POLY_EVERY 0
+#endif
+// every kPolyEvery-th probability pair of a row takes ex2_poly (0 = never)
+constexpr int kPolyEvery = FG_PREFILL_POLY_EVERY;
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -76,6 +119,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   const SeqInfo s = seq_info(a, b);
   const int m0 = m_block * BM;
   if (m0 >= s.q_len) return;  // before any allocation
+  // A wait that timed out anywhere on this device left the status word set: finish the
+  // launch quickly instead of letting every remaining CTA run into the same timeout
+  // (one thread reads it so that the whole CTA takes the same decision).
+  __shared__ int s_drain;
+  if (threadIdx.x == 0) s_drain = *reinterpret_cast<volatile int*>(a.status);
+  __syncthreads();
+  if (s_drain != 0) return;
 
   const int shift = s.k_len - s.q_len;
   int n_tiles = (s.k_len + BN - 1) / BN;
@@ -84,6 +134,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     n_tiles = lim <= 0 ? 0 : min(n_tiles, (lim + BN - 1) / BN);
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FG_PREFILL_TRACE
+  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) && (lane == 0);
+#endif
 
   if (n_tiles == 0) {
     // no visible key for any row of the block: zeros, lse = +inf
@@ -118,9 +171,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
   uint64_t* s_full = bars + 9;        // [2] per tile
-  uint64_t* p_ready = bars + 11;      // [2] per tile
-  uint64_t* o_done = bars + 13;       // [2] per tile
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* p_ready = bars + 11;      // [2 tiles][2 halves]
+  uint64_t* o_done = bars + 15;       // [2 tiles][2 halves]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
@@ -131,6 +184,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
+    }
+    for (int i = 0; i < 4; ++i) {
       mbar_init(&p_ready[i], 128);
       mbar_init(&o_done[i], 1);
     }
@@ -212,13 +267,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                      idesc_qk, k != 0 ? 1u : 0u);
         }
       };
-      auto issue_pv = [&](int t, int stg, bool acc) {
+      auto issue_pv_half = [&](int t, int stg, int h, bool acc) {
         const uint32_t va = smem_u32(sV + stg * TILE_BYTES);
 #pragma unroll
-        for (int k = 0; k < BN / 16; ++k) {
+        for (int k = 0; k < 4; ++k) {
           // V: MN-major, 64-column blocks HALF_BYTES apart, 8-key groups 1024 B apart, 16 keys per step
-          const uint64_t bdesc = umma_desc_sw128(va + k * 2048, HALF_BYTES, 1024);
-          mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + k * 8, bdesc, idesc_pv,
+          const uint64_t bdesc = umma_desc_sw128(va + (h * 4 + k) * 2048, HALF_BYTES, 1024);
+          mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + h * 64 + k * 8, bdesc, idesc_pv,
                      (acc || k != 0) ? 1u : 0u);
         }
       };
@@ -237,13 +292,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         const uint32_t ph = (uint32_t)((j >> 1) & 1);
         if (!mbar_wait(&v_full[stg], ph, abort_flag, a.status, st_code)) break;
         for (int t = 0; t < NT; ++t) {
-          if (!mbar_wait(&p_ready[t], (uint32_t)(j & 1), abort_flag, a.status, st_code)) {
-            ok = false;
-            break;
+          for (int h = 0; h < 2 && ok; ++h) {
+            if (!mbar_wait(&p_ready[t * 2 + h], (uint32_t)(j & 1), abort_flag, a.status, st_code)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            FG_TRACE(0 + t * 2 + h, j);
+            issue_pv_half(t, stg, h, j > 0 || h > 0);
+            tc_commit(&o_done[t * 2 + h]);
           }
-          tc_fence_after();
-          issue_pv(t, stg, j > 0);
-          tc_commit(&o_done[t]);
+          if (!ok) break;
           if (t == NT - 1) tc_commit(&v_empty[stg]);
           if (j + 1 < n_tiles) {
             const int nstg = (j + 1) & 1;
@@ -272,95 +331,114 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    for (int j = 0; j < n_tiles; ++j) {
+    const float scale = a.scale_log2;
+    for (int j = 0; j < n_tiles && ok; ++j) {
       if (!mbar_wait(&s_full[t], (uint32_t)(j & 1), abort_flag, a.status, st_code)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      float sv[128];
-      {
-        uint32_t* u = reinterpret_cast<uint32_t*>(sv);
-        tmem_ld32(s_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(u));
-        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(u + 32));
-        tmem_ld32(s_addr + 64, *reinterpret_cast<uint32_t(*)[32]>(u + 64));
-        tmem_ld32(s_addr + 96, *reinterpret_cast<uint32_t(*)[32]>(u + 96));
-        tmem_ld_wait();
-      }
-      const int col0 = j * BN;
-      const bool need_mask = (col0 + BN > s.k_len) || (a.causal && (col0 + BN - 1 > m0 + shift));
-      if (need_mask) {
-        int lim = s.k_len - 1;                        // last visible column
-        if (a.causal) lim = min(lim, qpos + shift);
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (col0 + i > lim) sv[i] = -INFINITY;
-      }
-      float mx = sv[0];
-#pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, sv[i]);
-      const float m_tile = mx * a.scale_log2;  // scale > 0; -inf stays -inf
-      // Raise the reference maximum only when it grows by more than the threshold:
-      // probabilities then stay below 2^8 and the accumulator needs no rescale.
-      const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
-      if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        if (!mbar_wait(&o_done[t], (uint32_t)((j - 1) & 1), abort_flag, a.status, st_code)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const float f = raise ? ex2(m_used - m_tile) : 1.0f;  // m_used == -inf -> 0 (accumulator is 0 there)
+      if (quarter == 0) FG_TRACE(4 + t * 16, j);
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(o_addr + c * 32, o);
+      for (int h = 0; h < 2; ++h) {
+        const uint32_t sh_addr = s_addr + h * 64;
+        float sv[64];
+        {
+          uint32_t* u = reinterpret_cast<uint32_t*>(sv);
+          tmem_ld32(sh_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(u));
+          tmem_ld32(sh_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(u + 32));
           tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-          tmem_st32(o_addr + c * 32, o);
         }
-        l_run *= f;
-      }
-      if (raise) m_used = m_tile;
-      const float m_safe = m_used == -INFINITY ? 0.f : m_used;
-      // probabilities in 4 chunks of 32 -> 16 packed 32-bit columns each, stored over S
-      float sum = 0.f;
+        const int col0 = j * BN + h * 64;
+        const bool need_mask = (col0 + 64 > s.k_len) || (a.causal && (col0 + 63 > m0 + shift));
+        if (need_mask) {
+          int lim = s.k_len - 1;                        // last visible column
+          if (a.causal) lim = min(lim, qpos + shift);
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2(fmaf(sv[c * 32 + 2 * i], a.scale_log2, -m_safe));
-          const float p1 = ex2(fmaf(sv[c * 32 + 2 * i + 1], a.scale_log2, -m_safe));
-          sum += p0 + p1;
-          pk[i] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
+          for (int i = 0; i < 64; ++i)
+            if (col0 + i > lim) sv[i] = -INFINITY;
         }
-        tmem_st16(s_addr + c * 16, pk);
-      }
-      l_run += sum;
-      tmem_st_wait();
-      tc_fence_before();
-      if (a.paged && t == 0 && j == n_tiles - 1 && col0 + BN > s.k_len) {
-        // Rows of the last V tile past the end of the sequence hold whatever the cache
-        // page holds; zero them so 0 * garbage can never produce NaN.
-        const int stg = j & 1;
-        if (mbar_wait(&v_full[stg], (uint32_t)((j >> 1) & 1), abort_flag, a.status, st_code)) {
-          const int first = s.k_len - col0;  // first invalid row of the tile
-          uint8_t* vt = sV + stg * TILE_BYTES;
-          for (int idx = r; idx < (BN - first) * 16; idx += 128) {
-            const int row = first + idx / 16, ch = idx % 16;
-            *reinterpret_cast<uint4*>(vt + (ch >> 3) * HALF_BYTES + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+        // four independent chains of three-input max
+        float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+        for (int i = 4; i < 64; i += 8) {
+          mx4[0] = max3(mx4[0], sv[i], sv[i + 1]);
+          mx4[1] = max3(mx4[1], sv[i + 2], sv[i + 3]);
+          if (i + 4 < 64) {
+            mx4[2] = max3(mx4[2], sv[i + 4], sv[i + 5]);
+            mx4[3] = max3(mx4[3], sv[i + 6], sv[i + 7]);
           }
-          fence_proxy_async_smem();
-        } else {
-          ok = false;
         }
+        const float m_tile = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * scale;  // scale > 0
+        // Raise the reference maximum only when it grows by more than the threshold:
+        // probabilities then stay below 2^8 and the accumulator needs no rescale.
+        const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
+        if ((j > 0 || h > 0) && __any_sync(0xffffffffu, raise)) {
+          // every PV issued so far must have landed: the last one is the previous half
+          const int ph = h ^ 1;
+          const int pj = h ? j : j - 1;
+          if (!mbar_wait(&o_done[t * 2 + ph], (uint32_t)(pj & 1), abort_flag, a.status, st_code)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const float f = raise ? ex2(m_used - m_tile) : 1.0f;  // m_used == -inf -> 0 (accumulator is 0 there)
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+            tmem_st32(o_addr + c * 32, o);
+          }
+          l_run *= f;
+        }
+        if (raise) m_used = m_tile;
+        const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+        // probabilities of this half: 2 chunks of 32 -> 16 packed 32-bit columns each
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const bool poly = kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1;
+            const float x0 = fmaf(sv[c * 32 + 2 * i], scale, neg_m);
+            const float x1 = fmaf(sv[c * 32 + 2 * i + 1], scale, neg_m);
+            const float p0 = poly ? ex2_poly(x0) : ex2(x0);
+            const float p1 = poly ? ex2_poly(x1) : ex2(x1);
+            sum4[i & 3] += p0 + p1;
+            pk[i] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
+          }
+          tmem_st16(sh_addr + c * 16, pk);
+        }
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tmem_st_wait();
+        tc_fence_before();
+        if (h == 0 && a.paged && t == 0 && j == n_tiles - 1 && j * BN + BN > s.k_len) {
+          // Rows of the last V tile past the end of the sequence hold whatever the cache
+          // page holds; zero them so 0 * garbage can never produce NaN.
+          const int stg = j & 1;
+          if (mbar_wait(&v_full[stg], (uint32_t)((j >> 1) & 1), abort_flag, a.status, st_code)) {
+            const int first = s.k_len - j * BN;  // first invalid row of the tile
+            uint8_t* vt = sV + stg * TILE_BYTES;
+            for (int idx = r; idx < (BN - first) * 16; idx += 128) {
+              const int row = first + idx / 16, ch = idx % 16;
+              *reinterpret_cast<uint4*>(vt + (ch >> 3) * HALF_BYTES + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+            }
+            fence_proxy_async_smem();
+          } else {
+            ok = false;
+          }
+        }
+        if (quarter == 0) FG_TRACE(5 + t * 16 + h, j);
+        mbar_arrive(&p_ready[t * 2 + h]);
+        if (!ok) break;
       }
-      mbar_arrive(&p_ready[t]);
-      if (!ok) break;
     }
 
-    if (ok && mbar_wait(&o_done[t], (uint32_t)((n_tiles - 1) & 1), abort_flag, a.status, st_code)) {
+    if (ok && mbar_wait(&o_done[t * 2 + 1], (uint32_t)((n_tiles - 1) & 1), abort_flag, a.status, st_code)) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       const bool valid = qpos < s.q_len;

@@ -87,6 +87,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // a timed-out wait earlier on this device: drain the launch instead of repeating it
+  // (one thread reads the word so that the whole CTA takes the same decision)
+  __shared__ int s_drain;
+  if (threadIdx.x == 0) s_drain = *reinterpret_cast<volatile int*>(g.status);
+  __syncthreads();
+  if (s_drain != 0) return;
 
   const int64_t tiles_m = (g.M + BM - 1) / BM;
   const int64_t tiles_n = (g.N + BN - 1) / BN;
@@ -331,7 +337,16 @@ int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
   g.has_bias = p->bias != nullptr;
   g.a_mn_major = a_mn; g.b_mn_major = b_mn;
   g.is_bf16 = p->dtype == FG_BF16;
-  g.group_m = 8;
+  // Row tiles per sweep over the column tiles: as many as keep the A panel of a group
+  // (group_m x 128 rows x K) around 32 MB, so that it stays L2-resident while B streams
+  // through once per group instead of once per 8 row tiles.
+  {
+    const int64_t panel = (int64_t)BM * p->K * 2;
+    int64_t gm = (32ll << 20) / (panel > 0 ? panel : 1);
+    if (gm < 4) gm = 4;
+    if (gm > 64) gm = 64;
+    g.group_m = (int)gm;
+  }
   g.c_vec_ok = aligned16(p->c) && (p->c_stride0 % 8 == 0);
   g.status = device_status_ptr();
   if (!g.status) return fail(FG_ERR_CUDA, "gemm: device status word unavailable");
