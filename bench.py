@@ -42,6 +42,7 @@ if str(ROOT) not in sys.path:
 METRIC = "inference operator-path throughput (fused_add_rms_norm, rope, silu_and_mul, varlen prefill, " \
          "cache write + paged decode, mm/addmm at the benchmark configs)"
 UNIT = "ops/s"
+NCCL_CTAS = 16  # SMs left to NCCL's copy kernels when N > 1
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -117,11 +118,15 @@ class ClockSampler:
 class Step:
     """The operators of one step with their inputs resident on ``device``."""
 
-    def __init__(self, device, rank: int, world: int, seed: int = 0, small: bool = False, only: str = ""):
+    def __init__(self, device, rank: int, world: int, seed: int = 0, small: bool = False, only: str = "",
+                 gather: str = "p2p"):
         import flaggems_b200 as fg
+        from flaggems_b200 import dist as fdist
         from flaggems_b200 import workloads as W
 
-        self.fg, self.W = fg, W
+        self.gather = gather
+
+        self.fg, self.W, self.fdist = fg, W, fdist
         self.device, self.rank, self.world = device, rank, world
         self.only = only
         s = seed + 1000 * rank  # every rank owns a different batch of sequences
@@ -147,9 +152,13 @@ class Step:
             c = torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=device)
             gathered = None
             if world > 1:
-                gathered = torch.empty((world * a.shape[0], b.shape[1]), dtype=a.dtype, device=device)
+                if gather == "nccl":
+                    gathered = torch.empty((world * a.shape[0], b.shape[1]), dtype=a.dtype, device=device)
+                else:
+                    gathered = fdist.PeerGather(c.shape, c.dtype, device)
             self.gemm[name] = (a, b, bias, c, gathered)
         self.comm_stream = torch.cuda.Stream(device=device) if world > 1 else None
+        self.comm_events = {}  # name -> (start, end) events of the last all-gather of that projection
         self.ops = self._build_ops()
 
     # each entry: (name, callable, work, kind) with kind "hbm" (bytes) or "tensor" (flops)
@@ -157,6 +166,16 @@ class Step:
         fg, W = self.fg, self.W
         T, H = self.x.shape
         ops = []
+        # The projections come first: with N > 1 their output shards are all-gathered on a side
+        # stream while the rest of the step runs (largest gather first).
+        for name in ("gate_up", "qkv", "down", "o"):
+            a, b, bias, c, gathered = self.gemm[name]
+            M, K = a.shape
+            N = b.shape[1]
+            if name in ("qkv", "gate_up"):  # qkv and gate_up carry a bias in the benchmark (addmm), o/down are mm
+                ops.append((f"addmm[{name}]", self._gemm_call(name, True), M * N * (2 * K + 1), "tensor"))
+            else:
+                ops.append((f"mm[{name}]", self._gemm_call(name, False), 2 * M * N * K, "tensor"))
         ops.append(("fused_add_rms_norm", lambda: fg.fused_add_rms_norm(self.x, self.res, [H], self.w, self.eps),
                     4 * T * H * 2 + H * 2, "hbm"))
         tq, hq, d = self.q.shape
@@ -184,13 +203,6 @@ class Step:
                                                       dd.max_seqlen_k, seqused_k=dd.seqused_k, causal=True,
                                                       block_table=dd.block_table, out=self.dec_out),
                     W.decode_bytes(dd.kv_lens, len(dd.kv_lens)), "hbm"))
-        for name, (a, b, bias, c, gathered) in self.gemm.items():
-            M, K = a.shape
-            N = b.shape[1]
-            if name in ("qkv", "gate_up"):  # qkv and gate_up carry a bias in the benchmark (addmm), o/down are mm
-                ops.append((f"addmm[{name}]", self._gemm_call(name, True), M * N * (2 * K + 1), "tensor"))
-            else:
-                ops.append((f"mm[{name}]", self._gemm_call(name, False), 2 * M * N * K, "tensor"))
         if self.only:
             ops = [o for o in ops if self.only in o[0]]
             if not ops:
@@ -210,8 +222,15 @@ class Step:
                 # column-parallel: gather the shards on the side stream; the next operators
                 # of the step overlap with the transfer, the step ends when all gathers have landed
                 self.comm_stream.wait_stream(torch.cuda.current_stream(self.device))
+                ev = self.comm_events.setdefault(
+                    name, (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
                 with torch.cuda.stream(self.comm_stream):
-                    torch.distributed.all_gather_into_tensor(gathered, c)
+                    ev[0].record()
+                    if self.gather == "nccl":
+                        torch.distributed.all_gather_into_tensor(gathered, c)
+                    else:
+                        gathered.push(c)
+                    ev[1].record()
         return run
 
     def run(self, events=None):
@@ -222,6 +241,9 @@ class Step:
             if events is not None:
                 events[i][1].record()
         if self.comm_stream is not None:
+            if self.gather != "nccl":
+                with torch.cuda.stream(self.comm_stream):
+                    next(iter(self.gemm.values()))[4].finish()  # one tiny all-reduce closes all pushes
             torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
 
     # ---------------- end-to-end form: host buffers in, host buffers out
@@ -349,7 +371,9 @@ def _workload_config(n_gpus):
                     " with cache write; mm/addmm M=8192 at qkv/o/gate_up/down",
         "ops_per_step": 10,
         "parallelism": "single GPU" if n_gpus == 1 else
-                       f"{n_gpus} ranks: sequences sharded with no exchange; projections column-parallel + NCCL all-gather",
+                       f"{n_gpus} ranks: sequences sharded with no exchange; projections column-parallel, shards "
+                       "all-gathered over NVLink beside the compute (copy-engine pushes + one NCCL all-reduce per step, "
+                       "or ncclAllGather with --gather nccl)",
         "l2": "no explicit flush: the step cycles through ~8 GB of operands, every operator's inputs are evicted "
               "from the 126 MB L2 between its consecutive invocations",
     }
@@ -365,6 +389,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (PCIe) leg")
     ap.add_argument("--only", default="", help="run only the operators whose name contains this string")
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: how the projection shards are gathered (copy-engine pushes into peer-mapped "
+                         "buffers closed by one NCCL all-reduce, or ncclAllGather)")
     ap.add_argument("--small", action="store_true",
                     help="reduced attention / GEMM sizes (for profiler captures); not a benchmark configuration")
     args = ap.parse_args()
@@ -382,14 +409,29 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    saved_stdout = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
+        if args.gather == "nccl":
+            # NCCL's all-gather kernels run beside the compute kernels: cap their CTAs and keep
+            # the persistent GEMM off the SMs they occupy
+            os.environ.setdefault("NCCL_MAX_CTAS", str(NCCL_CTAS))
+        # NCCL writes its banner to stdout; the contract is ONE JSON line there, so stdout is
+        # pointed at stderr until the result is printed
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
         torch.distributed.init_process_group("nccl", device_id=device)
 
     from flaggems_b200 import _lib
 
     peaks, peak_kind = load_peaks()
-    step = Step(device, rank, world, small=args.small, only=args.only)
+    if world > 1 and args.gather == "nccl":
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _lib.set_num_sms(sms - NCCL_CTAS)
+    step = Step(device, rank, world, small=args.small, only=args.only, gather=args.gather)
     n_ops = len(step.ops)
 
     def barrier():
@@ -474,9 +516,23 @@ def main():
         t, n, sample, detail = cpu_step_sample()
         out["cpu_baseline"] = {"value": n / t, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                "sample": sample, "step_seconds_scaled": t}
-    if rank == 0:
-        print(json.dumps(out))
     if world > 1:
+        gathers = []
+        for name, (g0, g1) in step.comm_events.items():
+            ms = g0.elapsed_time(g1)
+            g = step.gemm[name][4]
+            nbytes = (g.buf.numel() if hasattr(g, "buf") else g.numel()) * 2
+            gathers.append({"op": f"all_gather[{name}]", "ms": round(ms, 4), "bytes": nbytes,
+                            "busbw_GBs": round(nbytes * (world - 1) / world / ms / 1e6, 1)})
+        out["all_gather"] = gathers
+    if saved_stdout is not None:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        os.close(saved_stdout)
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        os.dup2(2, 1)  # anything NCCL prints while shutting down goes to stderr
         torch.distributed.destroy_process_group()
 
 

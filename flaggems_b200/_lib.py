@@ -83,6 +83,8 @@ SIGNATURES = {
     "fg_last_error": (C.c_char_p, []),
     "fg_launch_count": (C.c_int64, []),
     "fg_device_status": (C.c_int, [C.c_int]),
+    "fg_set_num_sms": (C.c_int, [C.c_int]),
+    "fg_get_num_sms": (C.c_int, []),
     "fg_fused_add_rms_norm": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, C.c_double, C.c_int, _P]),
     "fg_rms_norm": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, C.c_double, C.c_int, _P]),
     "fg_silu_and_mul": (C.c_int, [_P, _P, _P, C.c_int, _PI64, _PI64, _PI64, _PI64, C.c_int, _P]),
@@ -162,6 +164,11 @@ def stream_ptr(device: torch.device) -> int:
 
 def ptr(t) -> int | None:
     return None if t is None else t.data_ptr()
+
+
+def set_num_sms(sms: int) -> None:
+    """Limit the persistent kernels to ``sms`` SMs (0 = all); see ``fg_set_num_sms``."""
+    check(load().fg_set_num_sms(int(sms)))
 
 
 def launch_count() -> int:

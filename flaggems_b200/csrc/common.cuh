@@ -52,6 +52,10 @@ inline int num_sms() {
   return cached > 0 ? cached : 148;
 }
 
+// SMs the persistent kernels may occupy (fg_set_num_sms); the rest is left to kernels
+// that run beside them, e.g. NCCL's copy kernels.
+int sm_budget();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 inline int dtype_size(int dtype) { return dtype == FG_F32 ? 4 : 2; }

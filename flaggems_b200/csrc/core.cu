@@ -41,6 +41,22 @@ int* device_status_ptr() {
 
 }  // namespace fg
 
+namespace fg {
+std::atomic<int> g_sm_budget{0};  // 0 = use every SM of the device
+int sm_budget() {
+  const int n = num_sms();
+  const int b = g_sm_budget.load(std::memory_order_relaxed);
+  return (b > 0 && b < n) ? b : n;
+}
+}  // namespace fg
+
+extern "C" int fg_set_num_sms(int sms) {
+  if (sms < 0) return fg::fail(FG_ERR_INVALID, "fg_set_num_sms: negative SM count");
+  fg::g_sm_budget.store(sms, std::memory_order_relaxed);
+  return FG_OK;
+}
+extern "C" int fg_get_num_sms(void) { return fg::sm_budget(); }
+
 extern "C" int fg_abi_version(void) { return 1; }
 extern "C" const char* fg_last_error(void) { return fg::last_error_buf(); }
 extern "C" int64_t fg_launch_count(void) { return fg::g_launches.load(std::memory_order_relaxed); }

@@ -352,7 +352,7 @@ int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
   if (!g.status) return fail(FG_ERR_CUDA, "gemm: device status word unavailable");
 
   const int64_t tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN);
-  int grid = num_sms();
+  int grid = sm_budget();  // persistent: one CTA per SM it may use
   if (tiles < grid) grid = (int)tiles;
   if (p->dtype == FG_BF16) {
     static thread_local int attr_dev = -1;

@@ -7,7 +7,7 @@ all-gather of the output shards (NCCL on GPUs, gloo in the CPU tests).
 """
 from __future__ import annotations
 
-from typing import Tuple
+from typing import List, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -58,3 +58,68 @@ def all_gather_columns(local: torch.Tensor, world: int, group=None, out: torch.T
     buf = out if out is not None else torch.empty((world * M, n), dtype=local.dtype, device=local.device)
     dist.all_gather_into_tensor(buf.view(world * M, n), local.contiguous(), group=group)
     return buf.view(world, M, n).permute(1, 0, 2).reshape(M, world * n)
+
+
+class PeerGather:
+    """All-gather of equally shaped shards by copy-engine pushes over NVLink.
+
+    NCCL's all-gather runs on SMs and competes with the compute kernels it is meant to
+    overlap (a persistent GEMM loses whole waves when some SMs are taken).  Here every
+    rank owns a gather buffer ``[world, *shard_shape]`` in symmetric memory
+    (``torch.distributed._symmetric_memory``: the same allocation on every rank, mapped
+    into every peer's address space); ``push`` copies the local shard into slot ``rank``
+    of every peer's buffer with plain device-to-device copies (DMA engines, no SM; about
+    760 GB/s per direction on B200), and ``finish`` closes the round with one tiny NCCL
+    all-reduce on the same stream: when it completes on a rank, every rank has passed
+    its own copies, so all slots of the local buffer are filled.
+
+    On CPU tensors (gloo tests) it degrades to ``all_gather_into_tensor``.
+    The caller must not start the next round of pushes before the consumers of the
+    previous result are done with it.
+    """
+
+    def __init__(self, shard_shape, dtype, device, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        self.shard_shape = tuple(shard_shape)
+        self.peer_slots: List[Optional[torch.Tensor]] = [None] * self.world
+        self.use_p2p = self.device.type == "cuda" and self.world > 1
+        full = (self.world, *self.shard_shape)
+        if self.use_p2p:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self.buf = symm_mem.empty(full, dtype=dtype, device=self.device)
+            self._handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+            for p in range(self.world):
+                if p != self.rank:
+                    self.peer_slots[p] = self._handle.get_buffer(p, full, dtype)[self.rank]
+            self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+            dist.barrier(group=group)
+        else:
+            self.buf = torch.empty(full, dtype=dtype, device=self.device)
+
+    def push(self, local: torch.Tensor) -> None:
+        """Enqueue, on the current stream, the copies of ``local`` into every rank's slot."""
+        if not self.use_p2p:
+            if self.world == 1:
+                self.buf[0].copy_(local)
+            else:
+                dist.all_gather_into_tensor(self.buf.view(self.world * self.shard_shape[0], *self.shard_shape[1:]),
+                                            local.contiguous(), group=self.group)
+            return
+        self.buf[self.rank].copy_(local, non_blocking=True)
+        for i in range(1, self.world):  # staggered so that no peer is hit by everyone at once
+            p = (self.rank + i) % self.world
+            self.peer_slots[p].copy_(local, non_blocking=True)
+
+    def finish(self) -> None:
+        """Close a round of pushes (current stream): afterwards ``buf`` holds every shard."""
+        if self.use_p2p:
+            dist.all_reduce(self._token, group=self.group)
+
+    def columns(self) -> torch.Tensor:
+        """The gathered ``[M, world * n]`` matrix (a strided view of the buffer)."""
+        M, n = self.shard_shape
+        return self.buf.permute(1, 0, 2).reshape(M, self.world * n)

@@ -46,6 +46,13 @@ FG_API const char* fg_last_error(void);
 /* Number of kernels this library has launched since load (all threads). Used by
  * the benchmark to report how many of its own kernels ran in a timed region. */
 FG_API int64_t fg_launch_count(void);
+/* Persistent kernels (the tcgen05 GEMM) launch one CTA per SM and assume they get them
+ * all.  When communication kernels run beside them (NCCL all-gather on another stream)
+ * give the persistent kernels a smaller budget so that their CTAs are co-resident:
+ * fg_set_num_sms(n) limits them to n SMs for the whole process (0 = all SMs).
+ * No counterpart in the reference (it has no persistent kernels). */
+FG_API int fg_set_num_sms(int sms);
+FG_API int fg_get_num_sms(void);
 /* Device status word of the current device: 0 when healthy, otherwise the code a
  * kernel stored when one of its bounded waits (mbarrier / TMEM hand-off) ran out of
  * time and it returned early (101 = GEMM, 102 = attention prefill).  Synchronises

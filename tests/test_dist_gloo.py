@@ -31,6 +31,11 @@ def _worker(rank, world, port, ret):
         local = torch.addmm(bs, a, ws)
         full = fdist.all_gather_columns(local, world)
         ok_gemm = torch.allclose(full, torch.addmm(bias, a, w), atol=1e-5)
+        # the same through the gather object the GPU benchmark uses (collective fallback on CPU)
+        pg = fdist.PeerGather(local.shape, local.dtype, "cpu")
+        pg.push(local)
+        pg.finish()
+        ok_gemm = ok_gemm and torch.allclose(pg.columns(), torch.addmm(bias, a, w), atol=1e-5)
         # attention by KV head: each rank's output slice equals the same slice of the full result
         q = torch.randn(5, 8, 16, generator=g)
         k = torch.randn(5, 4, 16, generator=g)
