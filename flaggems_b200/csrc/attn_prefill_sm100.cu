@@ -5,21 +5,39 @@
 // tile, which halves the K/V traffic and lets the tensor pipe work on one tile while
 // the softmax warps work on the other.
 //
-//   warp 0       TMA producer: Q tiles once, then K and V tiles (128 keys x 128) through
+//   warps 0-7    softmax, one warpgroup per Q tile, one thread per row (TMEM lane = row), so a
+//                row needs no exchange between threads.  The score tile is produced in steps
+//                of 64 keys into two alternating TMEM buffers: while the warpgroup works on
+//                step i, the scores of step i+1 are already being computed.  Per step:
+//                tcgen05.ld the 64 scores once into registers, row max, scale, mask, exp2,
+//                pack P to 16 bit and tcgen05.st it over the first 32 columns of the buffer.
+//                The running max is only raised when it grows by more than 8 (log2 units),
+//                so the O accumulator in TMEM is rescaled rarely; the same warps write the
+//                normalised output
+//   warp 8       TMA producer: Q tiles once, then K and V tiles (128 keys x 128) through
 //                two 2-stage rings; paged caches are fetched page by page with one
 //                4-D box per page and 64-column half, so a tile lands as a dense,
 //                128-byte-swizzled K-major tile
-//   warp 1       issues tcgen05.mma from one thread: S_t = Q_t K^T as one SS group per 128
-//                keys (M128 N128, 8 x K16 -- an SS instruction costs ~115 cycles whatever
-//                its N, so N is kept at 128), and O_t += P_t V as TS MMAs (P read from TMEM
-//                as the A operand, full rate) in two halves of 64 keys
-//   warps 4-7    softmax of Q tile 0: one thread per row (TMEM lane = row), in two halves of
-//   warps 8-11   64 keys: tcgen05.ld the scores, scale, mask, exp2, pack P to 16 bit and
-//   (tile 1)     tcgen05.st it over the first 32 columns of that half; PV of the first half
-//                runs while the second half is exponentiated.  The running max is only
-//                raised when it grows by more than 8 (log2 units), so the O accumulator in
-//                TMEM is rescaled rarely; the same warps write the normalised output
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P halves alias S halves.
+//   warps 9,10   one tcgen05.mma issuing thread per Q tile: per step S = Q K^T as 8 SS MMAs
+//                (M128 N64 K16) and O += P V as 4 TS MMAs (M128 N128 K16, P read from TMEM as
+//                the A operand).  Order per tile: PV(i), then QK(i+2) into the buffer PV(i)
+//                has just released, so softmax(i+1) never waits for the tensor pipe's
+//                round trip.  Each tile has its own issuing thread so that one tile's MMAs do
+//                not queue behind the other's barrier waits
+// TMEM columns: tile t has score buffers at t*128 and t*128+64 and its output at 256+t*128;
+// P aliases the first 32 columns of its score buffer (keys [16k,16k+16) in columns 8k..8k+8).
+// Every wait in the kernel is an mbarrier wait with a time limit (no named barriers, no
+// register reallocation): a wait that gives up sets the device status word and the CTA drains.
+//
+// Measured costs that shaped this layout (B200, SM clocks, microbenchmarks on an otherwise
+// idle SM): an mbarrier arrive reaches a waiting thread after 110-150; the first result of
+// an MMA group lands ~180 after issue; the tensor pipe takes 59 for an SS M128 K16 MMA with
+// N <= 64, 64 with N = 128 (SS and TS alike), 128 with N = 256; one diverged thread needs
+// 45-50 to issue an MMA and ~95 for a tcgen05.commit; ex2 runs at 4 lanes per clock and
+// scheduler (8 per warp instruction), one warp alone sustains 12.5 per element of the
+// fma/ex2/add/pack mix and two or more warps per scheduler 8.3-8.7, i.e. the special-function
+// unit, not the tensor pipe, bounds a 128-wide head: 2048 clocks per 128 keys and two Q tiles
+// against 2080 of MMA time.
 //
 // Covers: fp16/bf16, head dim 128, causal or full attention, paged (block size a
 // power of two >= 8) or contiguous KV.  ALiBi, soft-cap, windows and other head dims
@@ -37,7 +55,9 @@ __device__ long long g_fg_trace[8192];
 extern "C" __attribute__((visibility("default"))) int fg_debug_read_trace(long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_fg_trace, sizeof(long long) * n);
 }
+#define FG_SITE(n) (st_code + 1000 * (n))
 #else
+#define FG_SITE(n) (st_code)
 #define FG_TRACE(slot, idx) \
   do {                      \
   } while (0)
@@ -49,10 +69,12 @@ int* device_status_ptr();
 
 namespace {
 
-constexpr int BM = 128, BN = 128, HD = 128;
+constexpr int BM = 128, BN = 128, HD = 128;   // BN: keys per K/V tile in shared memory
+constexpr int STEP = 64;                      // keys per score step (one TMEM score buffer)
 constexpr int HALF_BYTES = 128 * 64 * 2;   // one [128 x 64] 128B-swizzled sub-tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES; // 32 KB
-constexpr int NUM_THREADS = 384;
+constexpr int TMA_WARP = 8, MMA_WARP0 = 9;
+constexpr int NUM_THREADS = 11 * 32;   // 8 softmax warps, TMA producer, two MMA issuers
 constexpr int SMEM_BYTES = 6 * TILE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -70,25 +92,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA pipe (the MUFU unit, 4 lanes per clock and scheduler, is what the two
-// softmax warpgroups contend for): split x = n + f with a round-down add, evaluate a
-// cubic for 2^f on [0,1) and add n to the exponent field.  Relative error about 1e-4,
-// far below the 16-bit rounding of P.
-__device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.0f);
-  const float magic = 12582912.0f;                 // 1.5 * 2^23
-  const float xr = __fadd_rd(x, magic);            // integer part in the low mantissa bits
-  const float f = x - (xr - magic);                // [0, 1)
-  float p = fmaf(f, 0.077119873f, 0.227564394f);
-  p = fmaf(p, f, 0.695146143f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + ((__float_as_int(xr) - 0x4B400000) << 23));
-}
-#ifndef FG_PREFILL_POLY_EVERY
-#define FG_PREFILL_POLY_EVERY 0
-#endif
-// every kPolyEvery-th probability pair of a row takes ex2_poly (0 = never)
-constexpr int kPolyEvery = FG_PREFILL_POLY_EVERY;
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -128,11 +131,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   if (s_drain != 0) return;
 
   const int shift = s.k_len - s.q_len;
-  int n_tiles = (s.k_len + BN - 1) / BN;
-  if (a.causal) {
-    const int lim = m0 + BM + shift;  // exclusive bound on visible keys of this row block
-    n_tiles = lim <= 0 ? 0 : min(n_tiles, (lim + BN - 1) / BN);
-  }
+  int vis = s.k_len;                  // keys visible to at least one row of this block
+  if (a.causal) vis = max(0, min(vis, m0 + BM + shift));
+  const int n_steps = (vis + STEP - 1) / STEP;
+  const int n_tiles = (n_steps + 1) / 2;   // K/V tiles of 128 keys
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef FG_PREFILL_TRACE
   const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) && (lane == 0);
@@ -170,9 +172,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint64_t* k_empty = bars + 3;       // [2]
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2] per tile
-  uint64_t* p_ready = bars + 11;      // [2 tiles][2 halves]
-  uint64_t* o_done = bars + 15;       // [2 tiles][2 halves]
+  uint64_t* s_full = bars + 9;        // [2 tiles][2 score buffers]
+  uint64_t* p_ready = bars + 13;      // [2 tiles][2 score buffers]
+  uint64_t* o_done = bars + 17;       // [2 tiles]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -180,22 +182,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], NT);   // one commit per issuing thread
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
+      mbar_init(&v_empty[i], NT);
     }
-    for (int i = 0; i < 4; ++i) {
-      mbar_init(&p_ready[i], 128);
-      mbar_init(&o_done[i], 1);
-    }
+    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
+    for (int i = 0; i < 2; ++i) mbar_init(&o_done[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
   }
-  if (warp == 1) {
+  if (warp == MMA_WARP0) {
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
@@ -203,10 +203,19 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Register budget: 640 threads start with 96 registers each; the control warpgroup hands
+  // most of its share to the four softmax warpgroups, which keep 64 scores per thread live.
   const int hk = h0 / a.group;
   const int st_code = kStatusAttnTimeout;
+  // Every wait of a warp is polled by lane 0 and its outcome broadcast, so that a wait
+  // that gave up takes the whole warp the same way.
+  auto wwait = [&](uint64_t* bar, uint32_t parity, int site) -> bool {
+    int r = 1;
+    if (lane == 0) r = mbar_wait(bar, parity, abort_flag, a.status, FG_SITE(site)) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, r, 0) != 0;
+  };
 
-  if (warp == 0) {
+  if (warp == TMA_WARP) {
     // ================================ TMA producer ================================
     if (lane == 0) {
       mbar_expect_tx(q_full, NT * TILE_BYTES);
@@ -234,7 +243,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         uint64_t* empty = which ? &v_empty[stg] : &k_empty[stg];
         const CUtensorMap* tm = which ? &tmap_v : &tmap_k;
         uint8_t* dst = (which ? sV : sK) + stg * TILE_BYTES;
-        if (!mbar_wait(empty, ph ^ 1, abort_flag, a.status, st_code)) {
+        if (!wwait(empty, ph ^ 1, 1 + which)) {
           ok = false;
           break;
         }
@@ -251,194 +260,176 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         }
       }
     }
-  } else if (warp == 1) {
-    // ================================ MMA issuer ==================================
+  } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + NT) {
+    // ================================ MMA issuers =================================
+    // The descriptors are kept as 32-bit low words plus one constant high word so that an
+    // MMA costs one add per operand: the issuing thread shares its scheduler with four
+    // softmax warps and every instruction it spends is felt.
+    const int t = warp - MMA_WARP0;
     if (lane == 0) {
       const bool bf16 = pa.is_bf16 != 0;
-      const uint32_t idesc_qk = umma_idesc_f16(bf16, false, false, BM, BN);  // A, B K-major
-      const uint32_t idesc_pv = umma_idesc_f16(bf16, false, true, BM, HD);   // B (V) MN-major
-      auto issue_qk = [&](int t, int stg) {
-        const uint32_t qa = smem_u32(sQ + t * TILE_BYTES);
-        const uint32_t ka = smem_u32(sK + stg * TILE_BYTES);
+      const uint32_t idesc_qk = umma_idesc_f16(bf16, false, false, BM, STEP);  // A, B K-major, N = 64
+      const uint32_t idesc_pv = umma_idesc_f16(bf16, false, true, BM, HD);     // B (V) MN-major
+      // K-major operands: 8-row groups 1024 B apart.  V is MN-major: 64-column blocks HALF_BYTES
+      // apart (leading offset), 8-key groups 1024 B apart, 16 keys (2048 B) per MMA.
+      const uint32_t desc_hi = (uint32_t)(umma_desc_sw128(0, 0, 1024) >> 32);
+      const uint32_t q_lo = (uint32_t)umma_desc_sw128(smem_u32(sQ + t * TILE_BYTES), 0, 1024);
+      const uint32_t k_lo0 = (uint32_t)umma_desc_sw128(smem_u32(sK), 0, 1024);
+      const uint32_t v_lo0 = (uint32_t)umma_desc_sw128(smem_u32(sV), HALF_BYTES, 1024);
+      const uint32_t s_tmem = tmem_base + t * 128, o_tmem = tmem_base + 256 + t * 128;
+      bool ok = true;
+      // scores of step i: keys [64 i, 64 i + 64) = rows (i & 1) * 64 .. of K tile i >> 1
+      auto issue_qk = [&](int i) {
+        const int tile = i >> 1, stg = tile & 1;
+        if (!(i & 1) && !mbar_wait(&k_full[stg], (uint32_t)((tile >> 1) & 1), abort_flag, a.status, FG_SITE(8))) {
+          ok = false;
+          return;
+        }
+        tc_fence_after();
+        const uint32_t k_lo = k_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (STEP * 128 >> 4);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-          mma_f16_ss(tmem_base + t * 128, umma_desc_sw128(qa + off, 0, 1024), umma_desc_sw128(ka + off, 0, 1024),
-                     idesc_qk, k != 0 ? 1u : 0u);
+          const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+          mma_f16_ss_lohi(s_tmem + (i & 1) * STEP, q_lo + off, k_lo + off, desc_hi, idesc_qk, k != 0 ? 1u : 0u);
         }
+        tc_commit(&s_full[t * 2 + (i & 1)]);
+        FG_TRACE(48 + t, i);
+        if ((i & 1) || i == n_steps - 1) tc_commit(&k_empty[stg]);   // last step on this K tile
       };
-      auto issue_pv_half = [&](int t, int stg, int h, bool acc) {
-        const uint32_t va = smem_u32(sV + stg * TILE_BYTES);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          // V: MN-major, 64-column blocks HALF_BYTES apart, 8-key groups 1024 B apart, 16 keys per step
-          const uint64_t bdesc = umma_desc_sw128(va + (h * 4 + k) * 2048, HALF_BYTES, 1024);
-          mma_f16_ts(tmem_base + 256 + t * 128, tmem_base + t * 128 + h * 64 + k * 8, bdesc, idesc_pv,
-                     (acc || k != 0) ? 1u : 0u);
-        }
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag, a.status, st_code);
-      ok = ok && mbar_wait(&k_full[0], 0, abort_flag, a.status, st_code);
-      if (ok) {
+      ok = mbar_wait(q_full, 0, abort_flag, a.status, FG_SITE(3));
+      if (ok) issue_qk(0);
+      if (ok && n_steps > 1) issue_qk(1);
+      for (int i = 0; i < n_steps && ok; ++i) {
+        const int tile = i >> 1, stg = tile & 1;
+        if (!(i & 1) && !mbar_wait(&v_full[stg], (uint32_t)((tile >> 1) & 1), abort_flag, a.status, FG_SITE(5))) break;
+        if (!mbar_wait(&p_ready[t * 2 + (i & 1)], (uint32_t)((i >> 1) & 1), abort_flag, a.status, FG_SITE(6))) break;
         tc_fence_after();
-        for (int t = 0; t < NT; ++t) {
-          issue_qk(t, 0);
-          tc_commit(&s_full[t]);
-        }
-        tc_commit(&k_empty[0]);
-      }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int stg = j & 1;
-        const uint32_t ph = (uint32_t)((j >> 1) & 1);
-        if (!mbar_wait(&v_full[stg], ph, abort_flag, a.status, st_code)) break;
-        for (int t = 0; t < NT; ++t) {
-          for (int h = 0; h < 2 && ok; ++h) {
-            if (!mbar_wait(&p_ready[t * 2 + h], (uint32_t)(j & 1), abort_flag, a.status, st_code)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            FG_TRACE(0 + t * 2 + h, j);
-            issue_pv_half(t, stg, h, j > 0 || h > 0);
-            tc_commit(&o_done[t * 2 + h]);
-          }
-          if (!ok) break;
-          if (t == NT - 1) tc_commit(&v_empty[stg]);
-          if (j + 1 < n_tiles) {
-            const int nstg = (j + 1) & 1;
-            if (t == 0 && !mbar_wait(&k_full[nstg], (uint32_t)(((j + 1) >> 1) & 1), abort_flag, a.status, st_code)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            issue_qk(t, nstg);
-            tc_commit(&s_full[t]);
-            if (t == NT - 1) tc_commit(&k_empty[nstg]);
-          }
-        }
+        FG_TRACE(0 + t, i);
+        const uint32_t v_lo = v_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (4 * 2048 >> 4);
+        const uint32_t p_tmem = s_tmem + (i & 1) * STEP;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          mma_f16_ts_lohi(o_tmem, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&o_done[t]);
+        if ((i & 1) || i == n_steps - 1) tc_commit(&v_empty[stg]);     // last step on this V tile
+        if (i + 2 < n_steps) issue_qk(i + 2);
       }
     }
-  } else if (warp >= 4 && warp < 4 + 4 * NT) {
+  } else if (warp < 4 * NT) {
     // ================================ softmax / epilogue ===========================
-    const int t = (warp - 4) >> 2;
-    const int quarter = warp & 3;
+    const int t = warp >> 2;                  // Q tile
+    const int quarter = warp & 3;             // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;        // row inside the tile == TMEM lane
     const int qpos = m0 + r;                  // query position inside the sequence
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_addr = tmem_base + lane_addr + t * 128;
-    const uint32_t o_addr = tmem_base + lane_addr + 256 + t * 128;
+    const uint32_t s_addr = tmem_base + lane_addr + t * 128;         // my row of the score tile
+    const uint32_t o_addr = tmem_base + lane_addr + 256 + t * 128;   // my row of the output tile
     const bool bf16 = pa.is_bf16 != 0;
+    const float scale = a.scale_log2;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    const float scale = a.scale_log2;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      if (!mbar_wait(&s_full[t], (uint32_t)(j & 1), abort_flag, a.status, st_code)) {
+    for (int i = 0; i < n_steps; ++i) {
+      const int sb = i & 1;                              // score buffer of this step
+      const uint32_t sb_addr = s_addr + sb * STEP;
+      if (!wwait(&s_full[t * 2 + sb], (uint32_t)((i >> 1) & 1), 10)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      if (quarter == 0) FG_TRACE(4 + t * 16, j);
-#pragma unroll 1
-      for (int h = 0; h < 2; ++h) {
-        const uint32_t sh_addr = s_addr + h * 64;
-        float sv[64];
-        {
-          uint32_t* u = reinterpret_cast<uint32_t*>(sv);
-          tmem_ld32(sh_addr + 0, *reinterpret_cast<uint32_t(*)[32]>(u));
-          tmem_ld32(sh_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(u + 32));
-          tmem_ld_wait();
-        }
-        const int col0 = j * BN + h * 64;
-        const bool need_mask = (col0 + 64 > s.k_len) || (a.causal && (col0 + 63 > m0 + shift));
-        if (need_mask) {
-          int lim = s.k_len - 1;                        // last visible column
-          if (a.causal) lim = min(lim, qpos + shift);
+      if (quarter == 0) FG_TRACE(4 + t * 16, i);
+      float sv[64];
+      tmem_ld32(sb_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld32(sb_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+      tmem_ld_wait();
+      const int col0 = i * STEP;
+      if ((col0 + STEP > s.k_len) || (a.causal && (col0 + STEP - 1 > m0 + shift))) {
+        int lim = s.k_len - 1;                         // last visible column of this row
+        if (a.causal) lim = min(lim, qpos + shift);
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if (col0 + i > lim) sv[i] = -INFINITY;
-        }
-        // four independent chains of three-input max
-        float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
-#pragma unroll
-        for (int i = 4; i < 64; i += 8) {
-          mx4[0] = max3(mx4[0], sv[i], sv[i + 1]);
-          mx4[1] = max3(mx4[1], sv[i + 2], sv[i + 3]);
-          if (i + 4 < 64) {
-            mx4[2] = max3(mx4[2], sv[i + 4], sv[i + 5]);
-            mx4[3] = max3(mx4[3], sv[i + 6], sv[i + 7]);
-          }
-        }
-        const float m_tile = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]) * scale;  // scale > 0
-        // Raise the reference maximum only when it grows by more than the threshold:
-        // probabilities then stay below 2^8 and the accumulator needs no rescale.
-        const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
-        if ((j > 0 || h > 0) && __any_sync(0xffffffffu, raise)) {
-          // every PV issued so far must have landed: the last one is the previous half
-          const int ph = h ^ 1;
-          const int pj = h ? j : j - 1;
-          if (!mbar_wait(&o_done[t * 2 + ph], (uint32_t)(pj & 1), abort_flag, a.status, st_code)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const float f = raise ? ex2(m_used - m_tile) : 1.0f;  // m_used == -inf -> 0 (accumulator is 0 there)
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32(o_addr + c * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
-            tmem_st32(o_addr + c * 32, o);
-          }
-          l_run *= f;
-        }
-        if (raise) m_used = m_tile;
-        const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-        // probabilities of this half: 2 chunks of 32 -> 16 packed 32-bit columns each
-        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const bool poly = kPolyEvery > 0 && (i % (kPolyEvery > 0 ? kPolyEvery : 1)) == kPolyEvery - 1;
-            const float x0 = fmaf(sv[c * 32 + 2 * i], scale, neg_m);
-            const float x1 = fmaf(sv[c * 32 + 2 * i + 1], scale, neg_m);
-            const float p0 = poly ? ex2_poly(x0) : ex2(x0);
-            const float p1 = poly ? ex2_poly(x1) : ex2(x1);
-            sum4[i & 3] += p0 + p1;
-            pk[i] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
-          }
-          tmem_st16(sh_addr + c * 16, pk);
-        }
-        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        tmem_st_wait();
-        tc_fence_before();
-        if (h == 0 && a.paged && t == 0 && j == n_tiles - 1 && j * BN + BN > s.k_len) {
-          // Rows of the last V tile past the end of the sequence hold whatever the cache
-          // page holds; zero them so 0 * garbage can never produce NaN.
-          const int stg = j & 1;
-          if (mbar_wait(&v_full[stg], (uint32_t)((j >> 1) & 1), abort_flag, a.status, st_code)) {
-            const int first = s.k_len - j * BN;  // first invalid row of the tile
-            uint8_t* vt = sV + stg * TILE_BYTES;
-            for (int idx = r; idx < (BN - first) * 16; idx += 128) {
-              const int row = first + idx / 16, ch = idx % 16;
-              *reinterpret_cast<uint4*>(vt + (ch >> 3) * HALF_BYTES + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
-            }
-            fence_proxy_async_smem();
-          } else {
-            ok = false;
-          }
-        }
-        if (quarter == 0) FG_TRACE(5 + t * 16 + h, j);
-        mbar_arrive(&p_ready[t * 2 + h]);
-        if (!ok) break;
+        for (int e = 0; e < 64; ++e)
+          if (col0 + e > lim) sv[e] = -INFINITY;
       }
+      float m4[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+      for (int e = 4; e < 64; e += 8) {
+        m4[0] = max3(m4[0], sv[e], sv[e + 1]);
+        m4[1] = max3(m4[1], sv[e + 2], sv[e + 3]);
+        if (e + 4 < 64) {
+          m4[2] = max3(m4[2], sv[e + 4], sv[e + 5]);
+          m4[3] = max3(m4[3], sv[e + 6], sv[e + 7]);
+        }
+      }
+      const float m_tile = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]) * scale;  // scale > 0; -inf stays -inf
+      if (quarter == 0) FG_TRACE(6 + t * 16, i);
+      // Raise the reference maximum only when it grows by more than the threshold:
+      // probabilities then stay below 2^8 and the accumulator needs no rescale.
+      const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
+      if (i > 0 && __any_sync(0xffffffffu, raise)) {
+        // every PV issued so far (steps 0 .. i-1) must have landed before O is touched
+        if (!wwait(&o_done[t], (uint32_t)((i - 1) & 1), 14)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float f = raise ? ex2(m_used - m_tile) : 1.0f;  // m_used == -inf -> 0 (accumulator is 0 there)
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[32];
+          tmem_ld32(o_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+          tmem_st32(o_addr + c * 32, o);
+        }
+        l_run *= f;
+      }
+      if (raise) m_used = m_tile;
+      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+      if (a.paged && i == n_steps - 1 && col0 + STEP > s.k_len) {
+        // Rows of the last V tile past the end of the sequence hold whatever the cache
+        // page holds; zero the ones this step multiplies so 0 * garbage can never produce
+        // NaN.  Each Q tile does it for itself (same zeros twice): its PV is ordered after
+        // its own softmax only.
+        const int tile = i >> 1, stg = tile & 1;
+        if (!wwait(&v_full[stg], (uint32_t)((tile >> 1) & 1), 15)) {
+          ok = false;
+          break;
+        }
+        const int first = s.k_len - tile * BN;             // first invalid row of the tile
+        const int end = (i & 1) * STEP + STEP;             // this step's rows end here
+        uint8_t* vt = sV + stg * TILE_BYTES;
+        for (int idx = r; idx < (end - first) * 16; idx += 128) {
+          const int row = first + idx / 16, ch = idx % 16;
+          *reinterpret_cast<uint4*>(vt + (ch >> 3) * HALF_BYTES + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+      }
+      // ---- probabilities -> 32 packed 32-bit columns over the start of the score buffer
+      // (the scores are all in registers, so P may overwrite them in TMEM)
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float p0 = ex2(fmaf(sv[q * 32 + 2 * e], scale, neg_m));
+          const float p1 = ex2(fmaf(sv[q * 32 + 2 * e + 1], scale, neg_m));
+          sum4[e & 3] += p0 + p1;
+          pk[e] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
+        }
+        tmem_st16(sb_addr + q * 16, pk);
+      }
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (quarter == 0) FG_TRACE(40 + t * 8, i);
+      if (lane == 0) mbar_arrive(&p_ready[t * 2 + sb]);
     }
 
-    if (ok && mbar_wait(&o_done[t * 2 + 1], (uint32_t)((n_tiles - 1) & 1), abort_flag, a.status, st_code)) {
+    // ---- epilogue: normalise my row of O and write it out
+    if (ok && wwait(&o_done[t], (uint32_t)((n_steps - 1) & 1), 16)) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       const bool valid = qpos < s.q_len;
@@ -473,7 +464,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   // ================================ teardown ======================================
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == MMA_WARP0) {
     if (*abort_flag) {
       const uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
