@@ -174,8 +174,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint64_t* v_empty = bars + 7;       // [2]
   uint64_t* s_full = bars + 9;        // [2 tiles][2 score buffers]
   uint64_t* p_ready = bars + 13;      // [2 tiles][2 score buffers]
-  uint64_t* o_done = bars + 17;       // [2 tiles]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* o_done = bars + 17;       // [2 tiles][2]: PV of even / odd steps (a softmax warp can be two
+                                      // steps ahead of the tensor pipe, one parity bit per barrier is not enough)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
@@ -188,7 +189,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
     for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
     for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
-    for (int i = 0; i < 2; ++i) mbar_init(&o_done[i], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&o_done[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_q);
@@ -310,7 +311,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           mma_f16_ts_lohi(o_tmem, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&o_done[t]);
+        tc_commit(&o_done[t * 2 + (i & 1)]);
         if ((i & 1) || i == n_steps - 1) tc_commit(&v_empty[stg]);     // last step on this V tile
         if (i + 2 < n_steps) issue_qk(i + 2);
       }
@@ -366,8 +367,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       // probabilities then stay below 2^8 and the accumulator needs no rescale.
       const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
       if (i > 0 && __any_sync(0xffffffffu, raise)) {
-        // every PV issued so far (steps 0 .. i-1) must have landed before O is touched
-        if (!wwait(&o_done[t], (uint32_t)((i - 1) & 1), 14)) {
+        // every PV issued so far (steps 0 .. i-1; the pipe completes them in order) must have
+        // landed before O is touched
+        if (!wwait(&o_done[t * 2 + ((i - 1) & 1)], (uint32_t)(((i - 1) >> 1) & 1), 14)) {
           ok = false;
           break;
         }
@@ -429,7 +431,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
 
     // ---- epilogue: normalise my row of O and write it out
-    if (ok && wwait(&o_done[t], (uint32_t)((n_steps - 1) & 1), 16)) {
+    if (ok && wwait(&o_done[t * 2 + ((n_steps - 1) & 1)], (uint32_t)(((n_steps - 1) >> 1) & 1), 16)) {
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       const bool valid = qpos < s.q_len;

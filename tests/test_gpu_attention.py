@@ -211,6 +211,28 @@ def test_prefill_config3_full_size_properties(fg):
     torch.testing.assert_close(paged[first].float(), b.v[first].repeat_interleave(4, dim=1).float(), atol=1e-2, rtol=1e-2)
 
 
+def test_prefill_full_size_is_deterministic(fg):
+    # The kernel has no atomics and a fixed reduction order: repeated launches on the same
+    # inputs must agree bit for bit.  A difference means a missed wait between the tensor
+    # pipe and the softmax warps (one was caught this way: 32-row blocks read before the last
+    # PV had landed).
+    b = workloads.prefill_batch(seed=0, device=DEV)
+
+    def paged():
+        return fg.flash_attn_varlen_func(b.q, b.key_cache, b.value_cache, b.max_seqlen_q, b.cu_seqlens_q,
+                                         b.max_seqlen_k, seqused_k=b.seqused_k, causal=True, block_table=b.block_table)
+
+    def contig():
+        return fg.flash_attn_varlen_func(b.q, b.k, b.v, b.max_seqlen_q, b.cu_seqlens_q, b.max_seqlen_k,
+                                         cu_seqlens_k=b.cu_seqlens_k, causal=True)
+
+    for f in (paged, contig):
+        ref = f().clone()
+        for _ in range(10):
+            assert torch.equal(f(), ref)
+    assert torch.equal(paged(), contig())
+
+
 def test_decode_config4_reduced_with_cache_write(fg):
     # config-4 structure: write the new token with reshape_and_cache_flash, then decode
     b = workloads.decode_batch(seed=5, batch=24, min_ctx=30, max_ctx=2100, device=DEV)
