@@ -233,13 +233,19 @@ class Step:
                     ev[1].record()
         return run
 
-    def run(self, events=None):
+    def run(self, events=None, before=None, after=None):
+        """One step.  `before(i)` / `after(i)` run around operator i on the host (the
+        end-to-end form uses them to order the PCIe copies of that operator)."""
         for i, (_, fn, _, _) in enumerate(self.ops):
+            if before is not None:
+                before(i)
             if events is not None:
                 events[i][0].record()
             fn()
             if events is not None:
                 events[i][1].record()
+            if after is not None:
+                after(i)
         if self.comm_stream is not None:
             if self.gather != "nccl":
                 with torch.cuda.stream(self.comm_stream):
@@ -250,25 +256,66 @@ class Step:
     def make_e2e(self):
         """Pinned host copies of the per-step activations and host buffers for the results.
         Weights, cos/sin tables and the paged KV cache are resident state (they are not
-        inputs of a step in serving); everything a step consumes or produces crosses PCIe."""
+        inputs of a step in serving); everything a step consumes or produces crosses PCIe.
+        Each operator gets the list of tensors it consumes and produces, so that its uploads
+        can run on one copy engine and its downloads on the other while other operators
+        compute."""
         dd, p = self.dec, self.pre
-        ins = [self.x, self.res, self.q, self.k, self.pos, self.act, p.q, dd.q, dd.new_key, dd.new_value,
-               dd.slot_mapping] + [self.gemm[n][0] for n in self.gemm]
-        outs = [self.x, self.res, self.q, self.k, self.silu_out, self.pre_out, self.dec_out] + \
-               [self.gemm[n][3] for n in self.gemm]
-        self.h_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in ins]
-        self.h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outs]
-        self.e2e_in, self.e2e_out = ins, outs
-        h2d = sum(t.numel() * t.element_size() for t in ins)
-        d2h = sum(t.numel() * t.element_size() for t in outs)
+        io = {
+            "fused_add_rms_norm": ([self.x, self.res], [self.x, self.res]),
+            "rotary_embedding": ([self.q, self.k, self.pos], [self.q, self.k]),
+            "silu_and_mul": ([self.act], [self.silu_out]),
+            "flash_attn_varlen_func[prefill]": ([p.q], [self.pre_out]),
+            "reshape_and_cache_flash": ([dd.new_key, dd.new_value, dd.slot_mapping], []),
+            "flash_attn_varlen_func[decode]": ([dd.q], [self.dec_out]),
+        }
+        for n in self.gemm:
+            a, _, _, c, _ = self.gemm[n]
+            io[("addmm" if n in ("qkv", "gate_up") else "mm") + f"[{n}]"] = ([a], [c])
+        pin = lambda t, fill: (torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) if fill
+                               else torch.empty(t.shape, dtype=t.dtype, pin_memory=True))
+        self.e2e_plan = []
+        h2d = d2h = 0
+        for name, _, _, _ in self.ops:
+            ins, outs = io[name]
+            self.e2e_plan.append(([(pin(t, True), t) for t in ins], [(pin(t, False), t) for t in outs]))
+            h2d += sum(t.numel() * t.element_size() for t in ins)
+            d2h += sum(t.numel() * t.element_size() for t in outs)
+        self.h2d_stream = torch.cuda.Stream(device=self.device)
+        self.d2h_stream = torch.cuda.Stream(device=self.device)
+        self.e2e_in_ev = [torch.cuda.Event() for _ in self.ops]
+        self.e2e_out_ev = [torch.cuda.Event() for _ in self.ops]
         return h2d, d2h
 
     def run_e2e(self):
-        for h, d in zip(self.h_in, self.e2e_in):
-            d.copy_(h, non_blocking=True)
-        self.run()
-        for h, d in zip(self.h_out, self.e2e_out):
-            h.copy_(d, non_blocking=True)
+        """Host buffers -> step -> host buffers.  Uploads are queued operator by operator on
+        one stream, downloads on another, the operators on the current stream: operator i
+        starts when its inputs have landed and its results leave while later operators run."""
+        cur = torch.cuda.current_stream(self.device)
+        self.h2d_stream.wait_stream(cur)   # the previous step has consumed / downloaded its buffers
+        self.d2h_stream.wait_stream(cur)
+        with torch.cuda.stream(self.h2d_stream):
+            for i, (ins, _) in enumerate(self.e2e_plan):
+                for h, d in ins:
+                    d.copy_(h, non_blocking=True)
+                self.e2e_in_ev[i].record(self.h2d_stream)
+
+        def before(i):
+            cur.wait_event(self.e2e_in_ev[i])
+
+        def after(i):
+            outs = self.e2e_plan[i][1]
+            if not outs:
+                return
+            self.e2e_out_ev[i].record(cur)
+            with torch.cuda.stream(self.d2h_stream):
+                self.d2h_stream.wait_event(self.e2e_out_ev[i])
+                for h, d in outs:
+                    h.copy_(d, non_blocking=True)
+
+        self.run(before=before, after=after)
+        cur.wait_stream(self.d2h_stream)
+        cur.wait_stream(self.h2d_stream)
 
 
 # --------------------------------------------------------------------------- CPU arm
