@@ -318,6 +318,11 @@ class Step:
         cur.wait_stream(self.h2d_stream)
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one full-size launch under ncu
+# (profiles/gemm_tcgen05_kernel_gate_up_m2048.md, section "Full-size launch"): 630,821,888 + 447,437,312
+NCU_DRAM_BYTES_PER_LAUNCH = {"addmm[gate_up]": 1078259200}
+
+
 # --------------------------------------------------------------------------- CPU arm
 def cpu_step_sample(seed=0):
     """Time the CPU oracle on a bounded sample of one step; returns (scaled seconds for a
@@ -525,9 +530,13 @@ def main():
         per_op.append({"op": name, "ms": round(ms, 4), "bound": kind, "achieved": round(ach, 1), "unit": unit,
                        "peak": peak, "frac": round(ach / peak, 3)})
     dom = max(per_op, key=lambda o: o["ms"])
+    # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel
+    # from one ncu capture of the same launch; the captures are summarised under profiles/.
+    # Only full-size launches of the default workload have a figure.
+    traffic = None if args.small else NCU_DRAM_BYTES_PER_LAUNCH.get(dom["op"])
     roofline = {"bound": dom["bound"], "kernel": dom["op"], "achieved": dom["achieved"], "peak": dom["peak"],
                 "unit": dom["unit"], "frac": dom["frac"], "peak_source": peak_kind,
-                "traffic": None}
+                "traffic": traffic}
 
     # ---- end to end: pinned host buffers in and out, copies inside the timed region
     h2d = d2h = 0
