@@ -249,8 +249,7 @@ FG_API int fg_flash_attn_path(const fg_attn_params* p);
  *    FG_ERR_TOO_LARGE (need = chunks * batch * num_heads * (head_dim + 1) * 4 bytes, with
  *    chunks = ceil(max_seqlen_k / chunk) and chunk between 256 and 1024 tokens);
  *  - the first call on each device looks up the array's device address
- *    (cudaGetSymbolAddress, with that device current); make that first call before any
- *    stream capture is started;
+ *    (cudaGetSymbolAddress, with that device current) and keeps it;
  *  - all calls on a device share the one array, which keeps whatever the last call
  *    left in it.  Nothing in it has to start at zero (every slot that is read was
  *    written by the same call), but two calls that may run at the same time on one GPU
