@@ -109,6 +109,8 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+template <bool kBf16>   // element type of Q/K/V/P/out: bf16 or fp16 (a compile-time choice keeps the
+                        // per-pair conversions of the softmax loop free of selects)
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                             const __grid_constant__ CUtensorMap tmap_v, PrefillArgs pa) {
@@ -268,7 +270,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     // softmax warps and every instruction it spends is felt.
     const int t = warp - MMA_WARP0;
     if (lane == 0) {
-      const bool bf16 = pa.is_bf16 != 0;
+      constexpr bool bf16 = kBf16;
       const uint32_t idesc_qk = umma_idesc_f16(bf16, false, false, BM, STEP);  // A, B K-major, N = 64
       const uint32_t idesc_pv = umma_idesc_f16(bf16, false, true, BM, HD);     // B (V) MN-major
       // K-major operands: 8-row groups 1024 B apart.  V is MN-major: 64-column blocks HALF_BYTES
@@ -325,12 +327,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_addr + t * 128;         // my row of the score tile
     const uint32_t o_addr = tmem_base + lane_addr + 256 + t * 128;   // my row of the output tile
-    const bool bf16 = pa.is_bf16 != 0;
+    constexpr bool bf16 = kBf16;
     const float scale = a.scale_log2;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-    for (int i = 0; i < n_steps; ++i) {
+#ifdef FG_SKEW
+    if (NT == 2 && t == 1 && !wwait(&p_ready[0], 0, 18)) ok = false;   // experiment: start tile 1 half a step late
+#endif
+    for (int i = 0; i < n_steps && ok; ++i) {
       const int sb = i & 1;                              // score buffer of this step
       const uint32_t sb_addr = s_addr + sb * STEP;
       if (!wwait(&s_full[t * 2 + sb], (uint32_t)((i >> 1) & 1), 10)) {
@@ -536,12 +541,17 @@ int attn_prefill_sm100(const AttnArgs& a, int dtype, cudaStream_t st) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (attr_dev != dev) {
-    FG_CUDA_OK(cudaFuncSetAttribute(attn_prefill_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    FG_CUDA_OK(cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES));
+    FG_CUDA_OK(cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES));
     attr_dev = dev;
   }
   dim3 grid((a.max_q + BM - 1) / BM, a.H / pa.tiles, a.batch);
-  attn_prefill_tcgen05_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, pa);
+  if (pa.is_bf16)
+    attn_prefill_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, pa);
+  else
+    attn_prefill_tcgen05_kernel<false><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, pa);
   FG_CHECK_LAUNCH("attn_prefill_tcgen05_kernel");
   return FG_OK;
 }
