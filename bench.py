@@ -343,6 +343,94 @@ class Step:
 NCU_DRAM_BYTES_PER_LAUNCH = {"addmm[gate_up]": 1078259200}
 
 
+# --------------------------------------------------------------------------- reference GPU path
+def triton_reference_times(step, reps=5):
+    """Per-operator times of the unmodified reference (its Triton kernels, installed under
+    baseline/_ref) on the same device buffers; informational, only with --triton-ref.
+    Returns a list of {"op", "ms"} or a one-line reason why it could not run."""
+    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "flag_gems")):
+        return "reference install baseline/_ref is not present"
+    sys.path.insert(0, ref_dir)
+    try:
+        import flag_gems as ref
+    except Exception as e:  # noqa: BLE001
+        return f"reference does not import: {type(e).__name__}: {e}"
+    finally:
+        sys.path.remove(ref_dir)
+    import importlib
+
+    # (the packages re-export functions under the names of their modules, so fetch the modules by path)
+    silu_out = importlib.import_module("flag_gems.fused.silu_and_mul").silu_and_mul_out
+    mm_out = importlib.import_module("flag_gems.ops.mm").mm_out
+    addmm_out = importlib.import_module("flag_gems.ops.addmm").addmm_out
+    p, dd = step.pre, step.dec
+    H = step.x.shape[1]
+    a1, a2 = step.act[:, :step.half], step.act[:, step.half:]
+    calls = {
+        "fused_add_rms_norm": lambda: ref.fused_add_rms_norm(step.x, step.res, [H], step.w, step.eps),
+        "rotary_embedding": lambda: ref.apply_rotary_pos_emb(step.q, step.k, step.cos, step.sin, step.pos, False, True),
+        "silu_and_mul": lambda: silu_out(a1, a2, step.silu_out),
+        "flash_attn_varlen_func[prefill]": lambda: ref.flash_attn_varlen_func(
+            p.q, p.key_cache, p.value_cache, p.max_seqlen_q, p.cu_seqlens_q, p.max_seqlen_k, seqused_k=p.seqused_k,
+            causal=True, block_table=p.block_table, out=step.pre_out),
+        "reshape_and_cache_flash": lambda: ref.reshape_and_cache_flash(
+            dd.new_key, dd.new_value, dd.key_cache, dd.value_cache, dd.slot_mapping, "auto", None, None),
+        "flash_attn_varlen_func[decode]": lambda: ref.flash_attn_varlen_func(
+            dd.q, dd.key_cache, dd.value_cache, 1, dd.cu_seqlens_q, dd.max_seqlen_k, seqused_k=dd.seqused_k,
+            causal=True, block_table=dd.block_table, out=step.dec_out),
+    }
+    for n in step.gemm:
+        a, b, bias, c, _ = step.gemm[n]
+        if n in ("qkv", "gate_up"):
+            calls[f"addmm[{n}]"] = (lambda a=a, b=b, bias=bias, c=c: addmm_out(bias, a, b, out=c))
+        else:
+            calls[f"mm[{n}]"] = (lambda a=a, b=b, c=c: mm_out(a, b, out=c))
+    # The reference's launcher (utils/libentry.py:883-903) passes the argument list of Triton
+    # 3.3-3.5 when it re-launches a kernel from its own cache; with the Triton 3.6 of this image
+    # every second call of an operator fails with "function takes exactly N arguments".  The
+    # first call of a process (Triton's own JIT path) works, so its caches are emptied before
+    # each call -- run-time state only, the installed package is untouched.  That path has
+    # more host overhead; a short device-side sleep in front of the timed call lets the host
+    # run ahead, so the events bracket the reference's kernels and not its Python.
+    import gc
+
+    lib_entry_cls = importlib.import_module("flag_gems.utils.libentry").LibEntry
+
+    def forget():
+        for obj in gc.get_objects():
+            if isinstance(obj, lib_entry_cls):
+                for dev_cache in obj.kernel_cache:
+                    dev_cache.clear()
+
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=step.device)
+    out = []
+    for name, _, _, _ in step.ops:
+        fn = calls.get(name)
+        if fn is None:
+            continue
+        try:
+            for _ in range(2):   # includes the JIT build and the reference's autotuning
+                forget()
+                fn()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(reps):
+                forget()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                flush.zero_()                  # 512 MB written: the operator's operands leave the 126 MB L2
+                torch.cuda._sleep(4_000_000)   # ~2 ms of device time for the host to get ahead
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+            out.append({"op": name, "ms": round(statistics.median(times), 4)})
+        except Exception as e:  # noqa: BLE001
+            out.append({"op": name, "error": f"{type(e).__name__}: {str(e)[:120]}"})
+    return out
+
+
 # --------------------------------------------------------------------------- CPU arm
 def cpu_step_sample(seed=0):
     """Time the CPU oracle on a bounded sample of one step; returns (scaled seconds for a
@@ -461,6 +549,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (PCIe) leg")
     ap.add_argument("--only", default="", help="run only the operators whose name contains this string")
+    ap.add_argument("--triton-ref", action="store_true",
+                    help="N=1: also time the unmodified reference's Triton kernels (baseline/_ref) per operator; "
+                         "adds the reference's JIT and autotuning time to the run")
     ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: how the projection shards are gathered (copy-engine pushes into peer-mapped "
                          "buffers closed by one NCCL all-reduce, or ncclAllGather)")
@@ -590,6 +681,8 @@ def main():
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clocks, "per_op": per_op, "device_status": status,
     }
+    if rank == 0 and world == 1 and args.triton_ref:
+        out["triton_ref"] = triton_reference_times(step)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         t, n, sample, detail = cpu_step_sample()
         out["cpu_baseline"] = {"value": n / t, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",

@@ -332,10 +332,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
 
-#ifdef FG_SKEW
-    if (NT == 2 && t == 1 && !wwait(&p_ready[0], 0, 18)) ok = false;   // experiment: start tile 1 half a step late
-#endif
-    for (int i = 0; i < n_steps && ok; ++i) {
+    for (int i = 0; i < n_steps; ++i) {
       const int sb = i & 1;                              // score buffer of this step
       const uint32_t sb_addr = s_addr + sb * STEP;
       if (!wwait(&s_full[t * 2 + sb], (uint32_t)((i >> 1) & 1), 10)) {
