@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this folder from the reference checkout.
 
-Run it in a container that has the FlagGems tree (default ``/root/reference``):
+Run it on a machine that has the FlagGems tree:
 
-    python tests/golden/make_golden.py [--ref /path/to/FlagGems]
+    python tests/golden/make_golden.py --ref /path/to/FlagGems      (or FLAGGEMS_REF=/path/to/FlagGems)
 
 FlagGems' test modules import ``flag_gems`` at the top, which needs a GPU, so they
 cannot be imported on a CPU-only machine.  Their *oracle functions* are plain torch,
@@ -15,6 +15,7 @@ serve as fixed parity cases for the GPU tests.
 from __future__ import annotations
 
 import argparse
+import os
 import ast
 import random
 import types
@@ -45,7 +46,8 @@ def extract(path: Path, names, namespace):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("FLAGGEMS_REF"), required="FLAGGEMS_REF" not in os.environ,
+                    help="root of the FlagGems checkout the oracle functions are cut out of")
     args = ap.parse_args()
     ref = Path(args.ref)
     stub = types.SimpleNamespace(vendor_name="nvidia", device="cpu")
