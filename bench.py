@@ -343,6 +343,42 @@ class Step:
 NCU_DRAM_BYTES_PER_LAUNCH = {"addmm[gate_up]": 1078259200}
 
 
+# --------------------------------------------------------------------------- operators beyond the step
+def extra_op_times(device, peaks, reps=10):
+    """Operators of the next scope rows, timed on their own (not part of `value`):
+    aten::_flash_attention_forward on a dense causal GQA batch (8 x 4096 tokens, 32/8 heads,
+    d=128, bf16) in the packed layout and as the transposed views SDPA passes."""
+    import flaggems_b200 as fg
+
+    g = torch.Generator(device="cpu").manual_seed(77)
+    B, S, H, Hk, D = 8, 4096, 32, 8, 128
+    mk = lambda h: torch.randn((B, S, h, D), generator=g, dtype=torch.float32).to(device=device, dtype=torch.bfloat16)
+    q, k, v = mk(H), mk(Hk), mk(Hk)
+    flops = 4 * B * H * D * S * (S + 1) // 2
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    out = []
+    for label, args in (("packed (batch, seq, heads, dim)", (q, k, v)),
+                        ("transposed views of (batch, heads, seq, dim)",
+                         tuple(x.transpose(1, 2).contiguous().transpose(1, 2) for x in (q, k, v)))):
+        fn = lambda: fg.flash_attention_forward(*args, None, None, S, S, 0.0, True, False)
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        out.append({"op": f"_flash_attention_forward dense causal B{B} S{S} H{H}/{Hk} d{D}, {label}", "ms": round(ms, 4),
+                    "bound": "tensor", "achieved": round(flops / ms / 1e9, 1), "unit": "TFLOP/s",
+                    "peak": peaks["bf16_tflops_sustained"], "frac": round(flops / ms / 1e9 / peaks["bf16_tflops_sustained"], 3)})
+    return out
+
+
 # --------------------------------------------------------------------------- reference GPU path
 def triton_reference_times(step, reps=5):
     """Per-operator times of the unmodified reference (its Triton kernels, installed under
@@ -549,6 +585,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (PCIe) leg")
     ap.add_argument("--only", default="", help="run only the operators whose name contains this string")
+    ap.add_argument("--extra", action="store_true",
+                    help="N=1: also time the operators built beyond the benchmark step (dense _flash_attention_forward)")
     ap.add_argument("--triton-ref", action="store_true",
                     help="N=1: also time the unmodified reference's Triton kernels (baseline/_ref) per operator; "
                          "adds the reference's JIT and autotuning time to the run")
@@ -681,6 +719,8 @@ def main():
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clocks, "per_op": per_op, "device_status": status,
     }
+    if rank == 0 and world == 1 and args.extra:
+        out["extra_ops"] = extra_op_times(device, peaks)
     if rank == 0 and world == 1 and args.triton_ref:
         out["triton_ref"] = triton_reference_times(step)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:

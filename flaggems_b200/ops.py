@@ -18,7 +18,8 @@ from . import _lib
 
 logger = logging.getLogger("flag_gems." + __name__.split(".")[-1])
 
-__all__ = ["mm", "mm_out", "addmm", "addmm_out", "flash_attn_varlen_func", "rms_norm", "get_higher_dtype"]
+__all__ = ["mm", "mm_out", "addmm", "addmm_out", "flash_attn_varlen_func", "flash_attention_forward", "rms_norm",
+           "get_higher_dtype"]
 
 _ordered_datatypes = [torch.float16, torch.bfloat16, torch.float32]
 
@@ -336,3 +337,86 @@ def flash_attn_varlen_func(
             p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
         _lib.check(lib.fg_flash_attn_varlen(C.byref(p), _lib.stream_ptr(dev)))
     return (out, lse) if return_softmax_lse else out
+
+
+_cu_cache: dict = {}
+
+
+def _dense_cu_seqlens(batch: int, seqlen: int, device) -> torch.Tensor:
+    """``[0, S, 2S, ...]`` int32 on the device, cached per (batch, seqlen, device)."""
+    key = (batch, seqlen, device)
+    cu = _cu_cache.get(key)
+    if cu is None:
+        if len(_cu_cache) > 64:
+            _cu_cache.clear()
+        cu = torch.arange(0, (batch + 1) * seqlen, seqlen, dtype=torch.int32, device=device)
+        _cu_cache[key] = cu
+    return cu
+
+
+def flash_attention_forward(
+    query,
+    key,
+    value,
+    cumulative_sequence_length_q,
+    cumulative_sequence_length_k,
+    max_q,
+    max_k,
+    dropout_p,
+    is_causal,
+    return_debug_mask,
+    *,
+    scale=None,
+    softcap=0.0,
+    window_size_left=None,
+    window_size_right=None,
+    seqused_k=None,
+    alibi_slopes=None,
+    disable_splitkv=False,
+):
+    """``aten::_flash_attention_forward`` for dense batches, the override FlagGems installs
+    with ``enable()`` and ``F.scaled_dot_product_attention`` reaches on CUDA
+    (``src/flag_gems/ops/attention.py:1028-1110``, ``ops/flash_api.py:572-916``).
+
+    ``query`` is ``(batch, seqlen_q, heads, head_dim)``, ``key``/``value``
+    ``(batch, seqlen_k, kv_heads, head_dim)``; returns
+    ``(out, logsumexp (batch, heads, seqlen_q) fp32, rng_state, unused, debug_mask)``.
+    A dense batch is the packed form with equally long sequences, so the call goes to the
+    same kernels as ``flash_attn_varlen_func`` (tcgen05 prefill for head dim 128, split-KV
+    decode for single-token queries, the general kernel otherwise).  Like the reference the
+    varlen form of this ATen entry is not supported; unlike it, dropout is not either (this is
+    the inference path) and tensors whose batch and sequence dimensions do not pack (the
+    transposed views SDPA passes) are made contiguous first.
+    """
+    assert cumulative_sequence_length_q is None and cumulative_sequence_length_k is None, \
+        "varlen is not supported yet."
+    assert query.dim() == 4 and key.dim() == 4 and value.dim() == 4, "expected (batch, seqlen, heads, head_dim)"
+    hq, hk, hv = query.shape[-1], key.shape[-1], value.shape[-1]
+    assert hq == hk and hk == hv
+    assert hk in {16, 32, 64, 96, 128, 192, 256}
+    if dropout_p and dropout_p > 0.0:
+        raise NotImplementedError("flash_attention_forward: dropout is not part of the inference path")
+    B, Sq, H, D = query.shape
+    Sk = key.shape[1]
+    softmax_scale = scale or 1.0 / (D ** 0.5)
+
+    def packed(x):
+        # (batch, seq) -> one token dimension needs stride(0) == seq * stride(1) and unit inner stride
+        if x.stride(-1) == 1 and x.stride(0) == x.shape[1] * x.stride(1):
+            return x.as_strided((x.shape[0] * x.shape[1], x.shape[2], x.shape[3]), (x.stride(1), x.stride(2), 1),
+                                x.storage_offset())
+        return x.contiguous().view(x.shape[0] * x.shape[1], x.shape[2], x.shape[3])
+
+    q, k, v = packed(query), packed(key), packed(value)
+    out = torch.empty((B * Sq, H, D), dtype=query.dtype, device=query.device)
+    wl = -1 if window_size_left is None else int(window_size_left)
+    wr = -1 if window_size_right is None else int(window_size_right)
+    res, lse = flash_attn_varlen_func(
+        q, k, v, Sq, _dense_cu_seqlens(B, Sq, query.device), Sk, cu_seqlens_k=_dense_cu_seqlens(B, Sk, query.device),
+        softmax_scale=softmax_scale, causal=bool(is_causal), window_size=(wl, wr), softcap=softcap,
+        alibi_slopes=alibi_slopes, return_softmax_lse=True, out=out)
+    lse = lse.view(H, B, Sq).permute(1, 0, 2).contiguous()
+    rng_state = torch.zeros(2, dtype=torch.int64, device=query.device)
+    unused = torch.empty(0, dtype=torch.int64, device=query.device)
+    debug_mask = torch.empty(0, dtype=query.dtype, device=query.device)
+    return res.view(B, Sq, H, D), lse, rng_state, unused, debug_mask

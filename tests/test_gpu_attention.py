@@ -321,3 +321,67 @@ def test_decode_contiguous_kv_and_garbage_tail(fg):
     dirty = fg.flash_attn_varlen_func(b.q, kc, vc, 1, b.cu_seqlens_q, b.max_seqlen_k, seqused_k=b.seqused_k,
                                       causal=True, block_table=b.block_table)
     assert torch.equal(clean, dirty)
+
+
+# ---- aten::_flash_attention_forward (dense batches), reached from F.scaled_dot_product_attention
+def _sdpa_oracle(q, k, v, scale, causal):
+    """fp32 CPU math on (batch, heads, seq, dim) tensors; bottom-right aligned causal mask,
+    KV heads repeated for GQA (the reference's oracle: tests/test_attention_ops.py:200-229)."""
+    q, k, v = q.cpu().float(), k.cpu().float(), v.cpu().float()
+    g = q.shape[1] // k.shape[1]
+    k, v = k.repeat_interleave(g, dim=1), v.repeat_interleave(g, dim=1)
+    s = torch.einsum("bhqd,bhkd->bhqk", q, k) * scale
+    if causal:
+        sq, sk = q.shape[2], k.shape[2]
+        mask = torch.ones(sq, sk, dtype=torch.bool).triu(diagonal=sk - sq + 1)
+        s = s.masked_fill(mask, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)   # rows without a visible key
+    return torch.einsum("bhqk,bhkd->bhqd", p, v), torch.logsumexp(s, dim=-1)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 128, 2048), (4, 8, 1024, 128), (4, 8, 17, 1030), (2, 8, 1024, 1024)])
+@pytest.mark.parametrize("head_size", [64, 128, 192, 256])
+@pytest.mark.parametrize("is_causal", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_flash_attention_forward_dense(fg, shape, head_size, is_causal, dtype):
+    # shapes of tests/test_attention_ops.py:473-797 (square, non-square, q shorter and longer than k)
+    batch, heads, sq, sk = shape
+    torch.manual_seed(0)
+    q = torch.randn(batch, heads, sq, head_size, dtype=dtype, device=DEV)
+    k = torch.randn(batch, heads, sk, head_size, dtype=dtype, device=DEV)
+    v = torch.randn(batch, heads, sk, head_size, dtype=dtype, device=DEV)
+    scale = head_size ** -0.5
+    ref, ref_lse = _sdpa_oracle(q, k, v, scale, is_causal)
+    # the ATen entry takes (batch, seq, heads, dim): transposed views, as SDPA passes them
+    out, lse, seed, offset, dbg = fg.flash_attention_forward(
+        q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), None, None, sq, sk, 0.0, is_causal, False, scale=scale)
+    assert out.shape == (batch, sq, heads, head_size) and lse.shape == (batch, heads, sq)
+    torch.testing.assert_close(out.transpose(1, 2).cpu().float(), ref, atol=ATOL, rtol=RTOL)
+    finite = torch.isfinite(ref_lse)
+    torch.testing.assert_close(lse.cpu()[finite], ref_lse[finite], atol=2e-2, rtol=1e-2)
+
+
+def test_sdpa_through_use_gems_and_gqa(fg):
+    # F.scaled_dot_product_attention -> aten::_flash_attention_forward -> this library
+    torch.manual_seed(1)
+    q = torch.randn(2, 8, 512, 128, dtype=torch.bfloat16, device=DEV)
+    k = torch.randn(2, 8, 512, 128, dtype=torch.bfloat16, device=DEV)
+    v = torch.randn(2, 8, 512, 128, dtype=torch.bfloat16, device=DEV)
+    ref, _ = _sdpa_oracle(q, k, v, 128 ** -0.5, True)
+    before = _lib.launch_count()
+    with fg.use_gems():
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        with sdpa_kernel(backends=[SDPBackend.FLASH_ATTENTION]):
+            out = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+    assert _lib.launch_count() > before, "SDPA did not reach this library's kernels"
+    torch.testing.assert_close(out.cpu().float(), ref, atol=ATOL, rtol=RTOL)
+    # grouped-query form through the operator itself (packed layout, no copy)
+    qg = torch.randn(2, 256, 8, 128, dtype=torch.float16, device=DEV)
+    kg = torch.randn(2, 300, 2, 128, dtype=torch.float16, device=DEV)
+    vg = torch.randn(2, 300, 2, 128, dtype=torch.float16, device=DEV)
+    o, lse, *_ = fg.flash_attention_forward(qg, kg, vg, None, None, 256, 300, 0.0, True, False)
+    refg, _ = _sdpa_oracle(qg.transpose(1, 2), kg.transpose(1, 2), vg.transpose(1, 2), 128 ** -0.5, True)
+    torch.testing.assert_close(o.transpose(1, 2).cpu().float(), refg, atol=ATOL, rtol=RTOL)
+    with pytest.raises(NotImplementedError):
+        fg.flash_attention_forward(qg, kg, vg, None, None, 256, 300, 0.1, True, False)
