@@ -376,6 +376,28 @@ def extra_op_times(device, peaks, reps=10):
         out.append({"op": f"_flash_attention_forward dense causal B{B} S{S} H{H}/{Hk} d{D}, {label}", "ms": round(ms, 4),
                     "bound": "tensor", "achieved": round(flops / ms / 1e9, 1), "unit": "TFLOP/s",
                     "peak": peaks["bf16_tflops_sustained"], "frac": round(flops / ms / 1e9 / peaks["bf16_tflops_sustained"], 3)})
+    # gelu_and_mul on the silu_and_mul benchmark shape: halves of [4096, 22016], bf16
+    x = torch.randn((4096, 22016), generator=g, dtype=torch.float32).to(device=device, dtype=torch.bfloat16)
+    half = x.shape[1] // 2
+    nbytes = x.numel() * 2 + x.shape[0] * half * 2
+    for approximate in ("none", "tanh"):
+        fn = lambda: fg.gelu_and_mul(x[:, :half], x[:, half:], approximate)
+        with torch.no_grad():
+            for _ in range(3):
+                fn()
+            times = []
+            for _ in range(reps):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        out.append({"op": f"gelu_and_mul[{approximate}] halves of [4096, 22016] (incl. output allocation)",
+                    "ms": round(ms, 4), "bound": "hbm", "achieved": round(nbytes / ms / 1e6, 1), "unit": "GB/s",
+                    "peak": peaks["hbm_gbs"], "frac": round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 3)})
     return out
 
 
@@ -586,7 +608,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (PCIe) leg")
     ap.add_argument("--only", default="", help="run only the operators whose name contains this string")
     ap.add_argument("--extra", action="store_true",
-                    help="N=1: also time the operators built beyond the benchmark step (dense _flash_attention_forward)")
+                    help="N=1: also time the operators built beyond the benchmark step (dense _flash_attention_forward, "
+                         "gelu_and_mul)")
     ap.add_argument("--triton-ref", action="store_true",
                     help="N=1: also time the unmodified reference's Triton kernels (baseline/_ref) per operator; "
                          "adds the reference's JIT and autotuning time to the run")

@@ -88,6 +88,7 @@ SIGNATURES = {
     "fg_fused_add_rms_norm": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, C.c_double, C.c_int, _P]),
     "fg_rms_norm": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, C.c_double, C.c_int, _P]),
     "fg_silu_and_mul": (C.c_int, [_P, _P, _P, C.c_int, _PI64, _PI64, _PI64, _PI64, C.c_int, _P]),
+    "fg_gelu_and_mul": (C.c_int, [_P, _P, _P, C.c_int, _PI64, _PI64, _PI64, _PI64, C.c_int, C.c_int, _P]),
     "fg_rotary_embedding": (C.c_int, [C.POINTER(RopeParams), _P]),
     "fg_reshape_and_cache_flash": (C.c_int, [_P, _P, _P, _P, _P] + [_I64] * 10 + [C.c_int, _P]),
     "fg_gemm": (C.c_int, [C.POINTER(GemmParams), _P]),

@@ -1,4 +1,4 @@
-// silu_and_mul: out = silu(fp32(a)) * b  (HBM-bound elementwise).
+// silu_and_mul / gelu_and_mul: out = act(fp32(a)) * b  (HBM-bound elementwise).
 // Fast kernel: tensors viewed as [rows, cols] with unit column stride, 16-byte
 // packets, two packets of each operand in flight per thread.  Generic kernel:
 // up to 6 broadcast dimensions with arbitrary element strides.
@@ -18,14 +18,33 @@ __device__ __forceinline__ float silu_mul_fast(float x, float y) {
   const float hx = 0.5f * x;
   return fmaf(hx, t, hx) * y;
 }
-template <typename T>
-__device__ __forceinline__ float silu_mul_t(float x, float y) {
-  return sizeof(T) == 4 ? silu_mul_f32(x, y) : silu_mul_fast(x, y);
+// gelu(x) * y, exact (erf) and tanh forms, constants as in fused/gelu_and_mul.py:15-21,52-64
+__device__ __forceinline__ float gelu_none_mul(float x, float y) {
+  return 0.5f * x * (1.0f + erff(x * 0.7071067811f)) * y;
+}
+template <bool FAST>
+__device__ __forceinline__ float gelu_tanh_mul(float x, float y) {
+  const float u = x * 0.79788456f * (1.0f + 0.044715f * x * x);
+  float t;
+  if (FAST) {
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+  } else {
+    t = tanhf(u);
+  }
+  return 0.5f * x * (1.0f + t) * y;
+}
+// ACT: 0 silu, 1 gelu (erf), 2 gelu (tanh).  FAST (16-bit element types) takes the MUFU
+// approximations; fp32 tensors and the strided fallback take the precise forms.
+template <typename T, int ACT, bool FAST>
+__device__ __forceinline__ float act_mul_t(float x, float y) {
+  if (ACT == 1) return gelu_none_mul(x, y);
+  if (ACT == 2) return gelu_tanh_mul<FAST && sizeof(T) != 4>(x, y);
+  return (FAST && sizeof(T) != 4) ? silu_mul_fast(x, y) : silu_mul_f32(x, y);
 }
 
 // [rows, cols] view; IDX is uint32_t when the packet count allows it (one 32-bit
 // division per packet instead of a 64-bit one).
-template <typename T, int UNROLL, typename IDX>
+template <typename T, int UNROLL, typename IDX, int ACT>
 __global__ void __launch_bounds__(256)
 silu_mul_rows_kernel(const T* a, const T* b, T* out,
                      int64_t total_packs, int packs_per_row, int64_t a_stride, int64_t b_stride,
@@ -54,7 +73,7 @@ silu_mul_rows_kernel(const T* a, const T* b, T* out,
       Vec16<T>::unpack(pa[u], fa);
       Vec16<T>::unpack(pb[u], fb);
 #pragma unroll
-      for (int e = 0; e < E; ++e) fa[e] = silu_mul_t<T>(fa[e], fb[e]);
+      for (int e = 0; e < E; ++e) fa[e] = act_mul_t<T, ACT, true>(fa[e], fb[e]);
       stg16(out + ooff[u], Vec16<T>::pack(fa));
     }
   }
@@ -66,7 +85,7 @@ struct Strided6 {
   int ndim;
 };
 
-template <typename T>
+template <typename T, int ACT>
 __global__ void __launch_bounds__(256)
 silu_mul_strided_kernel(const T* a, const T* b, T* out,
                         int64_t total, Strided6 d) {
@@ -84,11 +103,11 @@ silu_mul_strided_kernel(const T* a, const T* b, T* out,
         oo += r * d.so[k];
       }
     }
-    out[oo] = Cvt<T>::from_f32(silu_mul_f32(Cvt<T>::to_f32(a[oa]), Cvt<T>::to_f32(b[ob])));
+    out[oo] = Cvt<T>::from_f32(act_mul_t<T, ACT, false>(Cvt<T>::to_f32(a[oa]), Cvt<T>::to_f32(b[ob])));
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 static int launch_silu_mul(const T* a, const T* b, T* out, int ndim, const int64_t* sizes,
                            const int64_t* sa, const int64_t* sb, const int64_t* so,
                            cudaStream_t st) {
@@ -125,10 +144,10 @@ static int launch_silu_mul(const T* a, const T* b, T* out, int ndim, const int64
     const int64_t blocks = (total_packs + 256 * UNROLL - 1) / (256 * UNROLL);
     if (blocks > 2147483647LL) return fail(FG_ERR_TOO_LARGE, "silu_and_mul: tensor too large");
     if (total_packs + 256 * UNROLL < 4294967295LL)
-      silu_mul_rows_kernel<T, UNROLL, uint32_t><<<(unsigned)blocks, 256, 0, st>>>(
+      silu_mul_rows_kernel<T, UNROLL, uint32_t, ACT><<<(unsigned)blocks, 256, 0, st>>>(
           a, b, out, total_packs, (int)(cols / E), ras, rbs, ros);
     else
-      silu_mul_rows_kernel<T, UNROLL, int64_t><<<(unsigned)blocks, 256, 0, st>>>(
+      silu_mul_rows_kernel<T, UNROLL, int64_t, ACT><<<(unsigned)blocks, 256, 0, st>>>(
           a, b, out, total_packs, (int)(cols / E), ras, rbs, ros);
     FG_CHECK_LAUNCH("silu_mul_rows_kernel");
     return FG_OK;
@@ -144,29 +163,49 @@ static int launch_silu_mul(const T* a, const T* b, T* out, int ndim, const int64
   int64_t blocks = (total + 255) / 256;
   const int64_t cap = (int64_t)num_sms() * 32;
   if (blocks > cap) blocks = cap;
-  silu_mul_strided_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, total, d);
+  silu_mul_strided_kernel<T, ACT><<<(unsigned)blocks, 256, 0, st>>>(a, b, out, total, d);
   FG_CHECK_LAUNCH("silu_mul_strided_kernel");
   return FG_OK;
 }
 
 }  // namespace fg
 
+namespace fg {
+static int act_and_mul(const char* what, int act, const void* a, const void* b, void* out, int ndim,
+                       const int64_t* sizes, const int64_t* a_strides, const int64_t* b_strides,
+                       const int64_t* o_strides, int dtype, void* stream) {
+  FG_REQUIRE(ndim >= 0 && ndim <= 6, "%s: ndim %d not in [0, 6]", what, ndim);
+  FG_REQUIRE(ndim == 0 || (sizes && a_strides && b_strides && o_strides), "%s: null shape/stride array", what);
+  for (int i = 0; i < ndim; ++i) {
+    FG_REQUIRE(sizes[i] >= 0, "%s: negative size", what);
+    if (sizes[i] == 0) return FG_OK;
+  }
+  FG_REQUIRE(a && b && out, "%s: null pointer", what);
+  FG_DISPATCH_FLOAT(dtype, T, {
+    switch (act) {
+      case 0: return (launch_silu_mul<T, 0>((const T*)a, (const T*)b, (T*)out, ndim, sizes, a_strides, b_strides,
+                                            o_strides, (cudaStream_t)stream));
+      case 1: return (launch_silu_mul<T, 1>((const T*)a, (const T*)b, (T*)out, ndim, sizes, a_strides, b_strides,
+                                            o_strides, (cudaStream_t)stream));
+      default: return (launch_silu_mul<T, 2>((const T*)a, (const T*)b, (T*)out, ndim, sizes, a_strides, b_strides,
+                                             o_strides, (cudaStream_t)stream));
+    }
+  });
+  return FG_OK;
+}
+}  // namespace fg
+
 extern "C" int fg_silu_and_mul(const void* a, const void* b, void* out, int ndim,
                                const int64_t* sizes, const int64_t* a_strides,
                                const int64_t* b_strides, const int64_t* o_strides, int dtype,
                                void* stream) {
-  using namespace fg;
-  FG_REQUIRE(ndim >= 0 && ndim <= 6, "silu_and_mul: ndim %d not in [0, 6]", ndim);
-  FG_REQUIRE(ndim == 0 || (sizes && a_strides && b_strides && o_strides),
-             "silu_and_mul: null shape/stride array");
-  for (int i = 0; i < ndim; ++i) {
-    FG_REQUIRE(sizes[i] >= 0, "silu_and_mul: negative size");
-    if (sizes[i] == 0) return FG_OK;
-  }
-  FG_REQUIRE(a && b && out, "silu_and_mul: null pointer");
-  FG_DISPATCH_FLOAT(dtype, T,
-                    return (launch_silu_mul<T>((const T*)a, (const T*)b, (T*)out, ndim, sizes,
-                                               a_strides, b_strides, o_strides,
-                                               (cudaStream_t)stream)));
-  return FG_OK;
+  return fg::act_and_mul("silu_and_mul", 0, a, b, out, ndim, sizes, a_strides, b_strides, o_strides, dtype, stream);
+}
+
+extern "C" int fg_gelu_and_mul(const void* a, const void* b, void* out, int ndim,
+                               const int64_t* sizes, const int64_t* a_strides,
+                               const int64_t* b_strides, const int64_t* o_strides, int approximate_tanh,
+                               int dtype, void* stream) {
+  return fg::act_and_mul("gelu_and_mul", approximate_tanh ? 2 : 1, a, b, out, ndim, sizes, a_strides, b_strides,
+                         o_strides, dtype, stream);
 }

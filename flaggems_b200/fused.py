@@ -22,7 +22,7 @@ __all__ = [
     "fused_add_rms_norm",
     "apply_rotary_pos_emb",
     "silu_and_mul",
-    "silu_and_mul_out",
+    "silu_and_mul_out", "gelu_and_mul",
     "reshape_and_cache_flash",
 ]
 
@@ -158,7 +158,8 @@ def apply_rotary_pos_emb(
 # ---------------------------------------------------------------------------
 # silu_and_mul  (src/flag_gems/fused/silu_and_mul.py:12-53)
 # ---------------------------------------------------------------------------
-def _silu_and_mul_launch(A, B, out):
+def _silu_and_mul_launch(A, B, out, gelu=None):
+    """``gelu``: None for silu, else the ``approximate`` string of gelu_and_mul."""
     dev = _lib.require_cuda(A, B, out)
     shape = out.shape
     if len(shape) > 6:
@@ -167,10 +168,16 @@ def _silu_and_mul_launch(A, B, out):
     nd = len(shape)
     arr = C.c_int64 * max(nd, 1)
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().fg_silu_and_mul(
-            Ae.data_ptr(), Be.data_ptr(), out.data_ptr(), nd,
-            arr(*shape), arr(*Ae.stride()), arr(*Be.stride()), arr(*out.stride()),
-            _lib.dtype_code(out.dtype), _lib.stream_ptr(dev)))
+        if gelu is None:
+            _lib.check(_lib.load().fg_silu_and_mul(
+                Ae.data_ptr(), Be.data_ptr(), out.data_ptr(), nd,
+                arr(*shape), arr(*Ae.stride()), arr(*Be.stride()), arr(*out.stride()),
+                _lib.dtype_code(out.dtype), _lib.stream_ptr(dev)))
+        else:
+            _lib.check(_lib.load().fg_gelu_and_mul(
+                Ae.data_ptr(), Be.data_ptr(), out.data_ptr(), nd,
+                arr(*shape), arr(*Ae.stride()), arr(*Be.stride()), arr(*out.stride()),
+                1 if gelu == "tanh" else 0, _lib.dtype_code(out.dtype), _lib.stream_ptr(dev)))
     return out
 
 
@@ -193,6 +200,22 @@ def silu_and_mul(A, B):
     shape = torch.broadcast_shapes(A.shape, B.shape)
     out = torch.empty(shape, dtype=dt, device=A.device)
     return _silu_and_mul_launch(A, B, out)
+
+
+def gelu_and_mul(x, y, approximate="none"):
+    """``gelu(x, approximate) * y`` with broadcasting (forward of
+    ``src/flag_gems/fused/gelu_and_mul.py:95-139``; the reference's autograd backward is
+    not part of the inference path: tensors that require grad are refused)."""
+    logger.debug("GEMS GELU AND MUL FORWARD")
+    if approximate not in ("none", "tanh"):
+        raise ValueError(f"Invalid approximate value: {approximate}")
+    _lib.require_cuda(x, y)
+    if torch.is_grad_enabled() and (x.requires_grad or y.requires_grad):
+        raise RuntimeError("gelu_and_mul: backward is not implemented (inference path); call under torch.no_grad()")
+    x, y, dt = _promote(x, y)
+    shape = torch.broadcast_shapes(x.shape, y.shape)
+    out = torch.empty(shape, dtype=dt, device=x.device)
+    return _silu_and_mul_launch(x, y, out, gelu=approximate)
 
 
 def silu_and_mul_out(A, B, out):

@@ -91,6 +91,17 @@ FG_API int fg_silu_and_mul(const void* a, const void* b, void* out, int ndim,
                            void* stream);
 
 /* ------------------------------------------------------------------------
+ * gelu_and_mul: out = gelu(fp32(a)) * b with the exact (erf) form or, when
+ * `approximate_tanh` is non-zero, the tanh form.  Replaces the forward of gelu_and_mul
+ * (src/flag_gems/fused/gelu_and_mul.py:15-21,52-64,95-105); shapes and strides as for
+ * fg_silu_and_mul.
+ * ---------------------------------------------------------------------- */
+FG_API int fg_gelu_and_mul(const void* a, const void* b, void* out, int ndim,
+                           const int64_t* sizes, const int64_t* a_strides,
+                           const int64_t* b_strides, const int64_t* o_strides, int approximate_tanh,
+                           int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
  * rotary_embedding: rotate q [T, Hq, D] and k [T, Hk, D] by cos/sin rows.
  * Replaces flag_gems::rotary_embedding / rotary_embedding_inplace
  * (lib/rotary_embedding.cpp:96-280) and apply_rotary_pos_emb

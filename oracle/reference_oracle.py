@@ -238,6 +238,12 @@ def silu_and_mul(x: torch.Tensor, y: torch.Tensor, upcast: torch.dtype = torch.f
     return torch.mul(torch.nn.functional.silu(x.to(upcast)), y.to(upcast))
 
 
+def gelu_and_mul(x: torch.Tensor, y: torch.Tensor, approximate: str = "none",
+                 upcast: torch.dtype = torch.float64) -> torch.Tensor:
+    """``gelu(x, approximate) * y`` on upcast inputs (tests/test_binary_pointwise_ops.py:962-978)."""
+    return torch.mul(torch.nn.functional.gelu(x.to(upcast), approximate=approximate), y.to(upcast))
+
+
 def mm(a: torch.Tensor, b: torch.Tensor, upcast: torch.dtype = torch.float64) -> torch.Tensor:
     """``torch.mm`` on upcast inputs (tests/test_blas_ops.py:129-132)."""
     return torch.mm(a.to(upcast), b.to(upcast))

@@ -150,6 +150,31 @@ def test_silu_and_mul(fg, shape, dtype):
     assert_close(out.cpu(), O.silu_and_mul(a.cpu(), b.cpu()), dtype)
 
 
+@pytest.mark.parametrize("shape", POINTWISE_SHAPES)
+@pytest.mark.parametrize("dtype", FLOAT_DTYPES)
+@pytest.mark.parametrize("approximate", ["none", "tanh"])
+def test_gelu_and_mul(fg, shape, dtype, approximate):
+    # forward of tests/test_binary_pointwise_ops.py:962-978
+    torch.manual_seed(0)
+    a = torch.randn(shape, dtype=dtype, device=DEV)
+    b = torch.randn(shape, dtype=dtype, device=DEV)
+    out = fg.gelu_and_mul(a, b, approximate)
+    assert out.dtype == dtype and out.shape == a.shape
+    assert_close(out.cpu(), O.gelu_and_mul(a.cpu(), b.cpu(), approximate), dtype)
+
+
+def test_gelu_and_mul_halves_and_errors(fg):
+    x = workloads.silu_inputs(seed=3, T=512, device=DEV)
+    d = x.shape[1] // 2
+    for approximate in ("none", "tanh"):
+        assert_close(fg.gelu_and_mul(x[:, :d], x[:, d:], approximate).cpu(),
+                     O.gelu_and_mul(x[:, :d].cpu(), x[:, d:].cpu(), approximate), torch.bfloat16)
+    with pytest.raises(ValueError):
+        fg.gelu_and_mul(x[:, :d], x[:, d:], "fast")
+    with pytest.raises(RuntimeError, match="backward"):
+        fg.gelu_and_mul(x[:, :d].clone().requires_grad_(), x[:, d:])
+
+
 def test_silu_and_mul_halves_broadcast_and_out(fg):
     x = workloads.silu_inputs(seed=3, T=512, device=DEV)
     d = x.shape[-1] // 2
