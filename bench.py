@@ -376,6 +376,26 @@ def extra_op_times(device, peaks, reps=10):
         out.append({"op": f"_flash_attention_forward dense causal B{B} S{S} H{H}/{Hk} d{D}, {label}", "ms": round(ms, 4),
                     "bound": "tensor", "achieved": round(flops / ms / 1e9, 1), "unit": "TFLOP/s",
                     "peak": peaks["bf16_tflops_sustained"], "frac": round(flops / ms / 1e9 / peaks["bf16_tflops_sustained"], 3)})
+    # bmm: 32 problems of 1024 x 1024 x 1024, bf16 (one launch)
+    a3 = torch.randn((32, 1024, 1024), generator=g, dtype=torch.float32).to(device=device, dtype=torch.bfloat16)
+    b3 = torch.randn((32, 1024, 1024), generator=g, dtype=torch.float32).to(device=device, dtype=torch.bfloat16)
+    fn = lambda: fg.bmm(a3, b3)
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    fl = 2 * 32 * 1024 ** 3
+    out.append({"op": "bmm 32 x [1024, 1024] x [1024, 1024] bf16 (incl. output allocation)", "ms": round(ms, 4),
+                "bound": "tensor", "achieved": round(fl / ms / 1e9, 1), "unit": "TFLOP/s",
+                "peak": peaks["bf16_tflops_sustained"], "frac": round(fl / ms / 1e9 / peaks["bf16_tflops_sustained"], 3)})
     # gelu_and_mul on the silu_and_mul benchmark shape: halves of [4096, 22016], bf16
     x = torch.randn((4096, 22016), generator=g, dtype=torch.float32).to(device=device, dtype=torch.bfloat16)
     half = x.shape[1] // 2
@@ -609,7 +629,7 @@ def main():
     ap.add_argument("--only", default="", help="run only the operators whose name contains this string")
     ap.add_argument("--extra", action="store_true",
                     help="N=1: also time the operators built beyond the benchmark step (dense _flash_attention_forward, "
-                         "gelu_and_mul)")
+                         "gelu_and_mul, bmm)")
     ap.add_argument("--triton-ref", action="store_true",
                     help="N=1: also time the unmodified reference's Triton kernels (baseline/_ref) per operator; "
                          "adds the reference's JIT and autotuning time to the run")

@@ -54,6 +54,7 @@ def _config():
         ("addmm.out", ops.addmm_out),
         ("mm", ops.mm),
         ("mm.out", ops.mm_out),
+        ("bmm", ops.bmm),
         ("_flash_attention_forward", ops.flash_attention_forward),
     )
 

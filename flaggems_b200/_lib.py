@@ -91,7 +91,9 @@ SIGNATURES = {
     "fg_gelu_and_mul": (C.c_int, [_P, _P, _P, C.c_int, _PI64, _PI64, _PI64, _PI64, C.c_int, C.c_int, _P]),
     "fg_rotary_embedding": (C.c_int, [C.POINTER(RopeParams), _P]),
     "fg_reshape_and_cache_flash": (C.c_int, [_P, _P, _P, _P, _P] + [_I64] * 10 + [C.c_int, _P]),
+    "fg_reshape_and_cache": (C.c_int, [_P, _P, _P, _P, _P] + [_I64] * 8 + [C.c_int, _P]),
     "fg_gemm": (C.c_int, [C.POINTER(GemmParams), _P]),
+    "fg_gemm_batched": (C.c_int, [C.POINTER(GemmParams)] + [_I64] * 5 + [_P]),
     "fg_gemm_uses_tcgen05": (C.c_int, [C.POINTER(GemmParams)]),
     "fg_flash_attn_varlen": (C.c_int, [C.POINTER(AttnParams), _P]),
     "fg_flash_attn_workspace_bytes": (C.c_int64, [_I64] * 5),

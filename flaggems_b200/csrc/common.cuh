@@ -40,6 +40,13 @@ inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_
     ::fg::count_launch();                                                            \
   } while (0)
 
+// Batch of independent GEMMs of one shape (bmm): element strides between consecutive
+// problems; batch == 1 is the plain GEMM.
+struct GemmBatch {
+  int64_t batch = 1;
+  int64_t a_bs = 0, b_bs = 0, c_bs = 0, bias_bs = 0;
+};
+
 inline int num_sms() {
   static thread_local int cached_dev = -1;
   static thread_local int cached = 0;

@@ -6,7 +6,7 @@
 
 namespace fg {
 
-int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st);
+int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st);
 bool gemm_tcgen05_eligible(const fg_gemm_params* p);
 
 namespace {
@@ -91,16 +91,8 @@ extern "C" int fg_gemm_uses_tcgen05(const fg_gemm_params* p) {
   return (p != nullptr && fg::gemm_tcgen05_eligible(p)) ? 1 : 0;
 }
 
-extern "C" int fg_gemm(const fg_gemm_params* p, void* stream) {
-  using namespace fg;
-  FG_REQUIRE(p != nullptr, "gemm: null params");
-  FG_REQUIRE(p->M >= 0 && p->N >= 0 && p->K >= 0, "gemm: negative size");
-  if (p->M == 0 || p->N == 0) return FG_OK;
-  FG_REQUIRE(p->c != nullptr, "gemm: null output");
-  FG_REQUIRE(p->K == 0 || (p->a && p->b), "gemm: null operand");
-  cudaStream_t st = (cudaStream_t)stream;
-  if (gemm_tcgen05_eligible(p)) return gemm_tcgen05(p, st);
-
+namespace fg {
+static int gemm_one(const fg_gemm_params* p, cudaStream_t st) {
   GArgs g;
   g.a = p->a; g.b = p->b; g.bias = p->bias; g.c = p->c;
   g.M = p->M; g.N = p->N; g.K = p->K;
@@ -114,5 +106,56 @@ extern "C" int fg_gemm(const fg_gemm_params* p, void* stream) {
   dim3 grid((unsigned)gx, (unsigned)gy);
   FG_DISPATCH_FLOAT(p->dtype, T, gemm_generic_kernel<T><<<grid, 256, 0, st>>>(g));
   FG_CHECK_LAUNCH("gemm_generic_kernel");
+  return FG_OK;
+}
+
+static int gemm_checked(const char* what, const fg_gemm_params* p) {
+  FG_REQUIRE(p != nullptr, "%s: null params", what);
+  FG_REQUIRE(p->M >= 0 && p->N >= 0 && p->K >= 0, "%s: negative size", what);
+  if (p->M == 0 || p->N == 0) return 1;  // nothing to do
+  FG_REQUIRE(p->c != nullptr, "%s: null output", what);
+  FG_REQUIRE(p->K == 0 || (p->a && p->b), "%s: null operand", what);
+  return FG_OK;
+}
+}  // namespace fg
+
+extern "C" int fg_gemm(const fg_gemm_params* p, void* stream) {
+  using namespace fg;
+  const int rc = gemm_checked("gemm", p);
+  if (rc != FG_OK) return rc < 0 ? rc : FG_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (gemm_tcgen05_eligible(p)) return gemm_tcgen05(p, GemmBatch(), st);
+  return gemm_one(p, st);
+}
+
+extern "C" int fg_gemm_batched(const fg_gemm_params* p, int64_t batch, int64_t a_batch_stride,
+                               int64_t b_batch_stride, int64_t c_batch_stride, int64_t bias_batch_stride,
+                               void* stream) {
+  using namespace fg;
+  const int rc = gemm_checked("gemm_batched", p);
+  if (rc != FG_OK) return rc < 0 ? rc : FG_OK;
+  FG_REQUIRE(batch >= 0, "gemm_batched: negative batch");
+  if (batch == 0) return FG_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  // One launch when the tensor-core path takes the shape and the batch strides keep every
+  // problem 16-byte aligned and fit a tensor map; else one generic launch per problem.
+  const bool strides_ok = batch == 1 || (a_batch_stride % 8 == 0 && b_batch_stride % 8 == 0 && a_batch_stride > 0 &&
+                                         b_batch_stride > 0 && batch <= 2147483647LL);
+  if (gemm_tcgen05_eligible(p) && strides_ok) {
+    GemmBatch bt;
+    bt.batch = batch; bt.a_bs = a_batch_stride; bt.b_bs = b_batch_stride; bt.c_bs = c_batch_stride;
+    bt.bias_bs = bias_batch_stride;
+    return gemm_tcgen05(p, bt, st);
+  }
+  const int64_t es = p->dtype == FG_F32 ? 4 : 2;
+  for (int64_t i = 0; i < batch; ++i) {
+    fg_gemm_params q = *p;
+    q.a = p->a ? (const char*)p->a + i * a_batch_stride * es : nullptr;
+    q.b = p->b ? (const char*)p->b + i * b_batch_stride * es : nullptr;
+    q.c = (char*)p->c + i * c_batch_stride * es;
+    q.bias = p->bias ? (const char*)p->bias + i * bias_batch_stride * es : nullptr;
+    const int r = gemm_tcgen05_eligible(&q) ? gemm_tcgen05(&q, GemmBatch(), st) : gemm_one(&q, st);
+    if (r != FG_OK) return r;
+  }
   return FG_OK;
 }

@@ -41,6 +41,8 @@ struct GemmArgs {
   int is_bf16;
   int group_m;
   int c_vec_ok;                // 16-byte stores legal for C
+  int64_t batch;               // independent problems sharing the shape (bmm); the tensor maps carry
+  int64_t c_bs, bias_bs;       // the batch as their third dimension, C and bias by these strides
   int* status;
 };
 
@@ -96,7 +98,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   const int64_t tiles_m = (g.M + BM - 1) / BM;
   const int64_t tiles_n = (g.N + BN - 1) / BN;
-  const int64_t num_tiles = tiles_m * tiles_n;
+  const int64_t tiles_per_batch = tiles_m * tiles_n;
+  const int64_t num_tiles = tiles_per_batch * g.batch;
   const int num_kb = (int)((g.K + BK - 1) / BK);
 
   if (threadIdx.x == 0) {
@@ -130,7 +133,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int64_t tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, g.group_m, tm, tn);
+        const int bi = (int)(tile / tiles_per_batch);
+        tile_coords(tile - bi * tiles_per_batch, tiles_m, tiles_n, g.group_m, tm, tn);
         const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, kStatusGemmTimeout)) {
@@ -142,18 +146,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int k0 = kb * BK;
           if (!g.a_mn_major) {
-            tma_load_2d(sa, &tmap_a, &full_bar[stage], k0, m0);
+            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, m0, bi);
           } else {
 #pragma unroll
             for (int b = 0; b < BM / 64; ++b)
-              tma_load_2d(sa + b * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + 64 * b, k0);
+              tma_load_3d(sa + b * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + 64 * b, k0, bi);
           }
           if (!g.b_mn_major) {
-            tma_load_2d(sb, &tmap_b, &full_bar[stage], k0, n0);
+            tma_load_3d(sb, &tmap_b, &full_bar[stage], k0, n0, bi);
           } else {
 #pragma unroll
             for (int b = 0; b < BN / 64; ++b)
-              tma_load_2d(sb + b * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + 64 * b, k0);
+              tma_load_3d(sb + b * (64 * BK * 2), &tmap_b, &full_bar[stage], n0 + 64 * b, k0, bi);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -211,14 +215,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int buf = (int)(local & 1);
       const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, g.group_m, tm, tn);
+      const int64_t bi = tile / tiles_per_batch;
+      tile_coords(tile - bi * tiles_per_batch, tiles_m, tiles_n, g.group_m, tm, tn);
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, g.status, kStatusGemmTimeout)) break;
       tc_fence_after();
       const int64_t row = tm * BM + quarter * 32 + lane;
       const int64_t col0 = tn * BN;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-      T* crow = reinterpret_cast<T*>(g.c) + row * g.c_s0;
-      const T* bias = reinterpret_cast<const T*>(g.bias);
+      T* crow = reinterpret_cast<T*>(g.c) + bi * g.c_bs + row * g.c_s0;
+      const T* bias = reinterpret_cast<const T*>(g.bias) + bi * g.bias_bs;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -297,7 +302,7 @@ static bool tcgen05_eligible(const fg_gemm_params* p) {
   return true;
 }
 
-int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
+int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) {
   using namespace fg;
   // A: K-major if a_stride1 == 1 (row-major), else M-major.  Degenerate shapes with
   // both strides 1 are treated as row-major.
@@ -307,8 +312,11 @@ int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
 
   CUtensorMap ta, tb;
   {
-    uint64_t dims[2], strides[1];
-    uint32_t box[2];
+    // third dimension: the batch (extent 1 and a dummy stride for a plain GEMM)
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    dims[2] = (uint64_t)bt.batch;
+    box[2] = 1;
     if (!a_mn) {
       dims[0] = (uint64_t)p->K; dims[1] = (uint64_t)p->M; strides[0] = (uint64_t)p->a_stride0 * 2;
       box[0] = 64; box[1] = BM;
@@ -316,7 +324,8 @@ int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
       dims[0] = (uint64_t)p->M; dims[1] = (uint64_t)p->K; strides[0] = (uint64_t)p->a_stride1 * 2;
       box[0] = 64; box[1] = BK;
     }
-    int rc = encode_tmap_16bit(&ta, p->a, 2, dims, strides, box);
+    strides[1] = bt.batch > 1 ? (uint64_t)bt.a_bs * 2 : strides[0] * dims[1];
+    int rc = encode_tmap_16bit(&ta, p->a, 3, dims, strides, box);
     if (rc != FG_OK) return rc;
     if (!b_mn) {
       dims[0] = (uint64_t)p->K; dims[1] = (uint64_t)p->N; strides[0] = (uint64_t)p->b_stride1 * 2;
@@ -325,7 +334,8 @@ int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
       dims[0] = (uint64_t)p->N; dims[1] = (uint64_t)p->K; strides[0] = (uint64_t)p->b_stride0 * 2;
       box[0] = 64; box[1] = BK;
     }
-    rc = encode_tmap_16bit(&tb, p->b, 2, dims, strides, box);
+    strides[1] = bt.batch > 1 ? (uint64_t)bt.b_bs * 2 : strides[0] * dims[1];
+    rc = encode_tmap_16bit(&tb, p->b, 3, dims, strides, box);
     if (rc != FG_OK) return rc;
   }
   GemmArgs g;
@@ -347,11 +357,12 @@ int gemm_tcgen05(const fg_gemm_params* p, cudaStream_t st) {
     if (gm > 64) gm = 64;
     g.group_m = (int)gm;
   }
-  g.c_vec_ok = aligned16(p->c) && (p->c_stride0 % 8 == 0);
+  g.c_vec_ok = aligned16(p->c) && (p->c_stride0 % 8 == 0) && (bt.batch == 1 || bt.c_bs % 8 == 0);
+  g.batch = bt.batch; g.c_bs = bt.c_bs; g.bias_bs = bt.bias_bs;
   g.status = device_status_ptr();
   if (!g.status) return fail(FG_ERR_CUDA, "gemm: device status word unavailable");
 
-  const int64_t tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN);
+  const int64_t tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN) * bt.batch;
   int grid = sm_budget();  // persistent: one CTA per SM it may use
   if (tiles < grid) grid = (int)tiles;
   if (p->dtype == FG_BF16) {

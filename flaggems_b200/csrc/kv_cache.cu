@@ -62,6 +62,35 @@ __global__ void __launch_bounds__(256) cache_scatter_scalar_kernel(CacheArgs a) 
   }
 }
 
+// ---- vLLM v0 cache layout: K [blocks, heads, D/x, block_size, x], V [blocks, heads, D, block_size]
+// (contiguous).  One thread per element of a token row and K|V; the x-element groups of K
+// land as contiguous runs, V elements are block_size apart by the layout's definition.
+template <typename U>
+__global__ void __launch_bounds__(256) cache_scatter_v0_kernel(const U* key, const U* value, U* kc, U* vc,
+                                                               const int64_t* slots, int64_t T, int64_t H, int64_t D,
+                                                               int64_t BS, int64_t NB, int64_t X, int64_t ks,
+                                                               int64_t vs) {
+  const int64_t n = H * D;
+  const int64_t total = T * n * 2;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t tk = idx / n;
+    const int64_t i = idx - tk * n;
+    const int64_t tok = tk >> 1;
+    const bool which = tk & 1;
+    const int64_t slot = slots[tok];
+    if (slot < 0 || slot >= NB * BS) continue;  // padding, or outside the cache
+    const int64_t h = i / D, d = i - h * D;
+    const int64_t blk = slot / BS, off = slot - blk * BS;
+    if (!which) {
+      const int64_t xi = d / X, xo = d - xi * X;
+      kc[(((blk * H + h) * (D / X) + xi) * BS + off) * X + xo] = key[tok * ks + i];
+    } else {
+      vc[((blk * H + h) * D + d) * BS + off] = value[tok * vs + i];
+    }
+  }
+}
+
 }  // namespace fg
 
 extern "C" int fg_reshape_and_cache_flash(const void* key, const void* value, void* key_cache,
@@ -116,5 +145,38 @@ extern "C" int fg_reshape_and_cache_flash(const void* key, const void* value, vo
     }
     FG_CHECK_LAUNCH("cache_scatter_scalar_kernel");
   }
+  return FG_OK;
+}
+
+extern "C" int fg_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
+                                    const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                                    int64_t head_size, int64_t block_size, int64_t num_blocks, int64_t x,
+                                    int64_t key_stride, int64_t value_stride, int elem_size, void* stream) {
+  using namespace fg;
+  FG_REQUIRE(num_tokens >= 0 && num_heads >= 0 && head_size >= 0, "reshape_and_cache: negative size");
+  FG_REQUIRE(block_size > 0 && num_blocks >= 0, "reshape_and_cache: block_size must be positive");
+  FG_REQUIRE(x > 0 && head_size % x == 0, "reshape_and_cache: head_size %lld is not a multiple of x = %lld",
+             (long long)head_size, (long long)x);
+  FG_REQUIRE(elem_size == 1 || elem_size == 2 || elem_size == 4, "reshape_and_cache: element size %d not in {1,2,4}",
+             elem_size);
+  if (num_tokens == 0 || num_heads * head_size == 0) return FG_OK;
+  FG_REQUIRE(key && value && key_cache && value_cache && slot_mapping, "reshape_and_cache: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t total = num_tokens * num_heads * head_size * 2;
+  int64_t blocks = (total + 255) / 256;
+  const int64_t cap = (int64_t)num_sms() * 32;
+  if (blocks > cap) blocks = cap;
+#define FG_V0(U)                                                                                              \
+  cache_scatter_v0_kernel<U><<<(unsigned)blocks, 256, 0, st>>>((const U*)key, (const U*)value, (U*)key_cache,   \
+                                                               (U*)value_cache, slot_mapping, num_tokens,     \
+                                                               num_heads, head_size, block_size, num_blocks, x, \
+                                                               key_stride, value_stride)
+  switch (elem_size) {
+    case 1: FG_V0(uint8_t); break;
+    case 2: FG_V0(uint16_t); break;
+    default: FG_V0(uint32_t); break;
+  }
+#undef FG_V0
+  FG_CHECK_LAUNCH("cache_scatter_v0_kernel");
   return FG_OK;
 }

@@ -24,6 +24,7 @@ __all__ = [
     "silu_and_mul",
     "silu_and_mul_out", "gelu_and_mul",
     "reshape_and_cache_flash",
+    "reshape_and_cache",
 ]
 
 
@@ -273,4 +274,43 @@ def reshape_and_cache_flash(
             slot_mapping.data_ptr(), num_tokens, num_heads, head_size, block_size, key_cache.size(0),
             key.stride(0), value.stride(0), key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
             key.element_size(), _lib.stream_ptr(dev)))
+    return None
+
+
+def reshape_and_cache(
+    key,           # [num_tokens, num_heads, head_size]
+    value,         # [num_tokens, num_heads, head_size]
+    key_cache,     # [num_blocks, num_heads, head_size/x, block_size, x]
+    value_cache,   # [num_blocks, num_heads, head_size, block_size]
+    slot_mapping,  # [num_tokens]
+    kv_cache_dtype,
+    k_scale,
+    v_scale,
+):
+    """Scatter new K/V tokens into the vLLM v0 cache layout
+    (``src/flag_gems/fused/reshape_and_cache.py:70-106``).  ``kv_cache_dtype``, ``k_scale``
+    and ``v_scale`` are accepted and ignored, as in the reference.  Returns None."""
+    logger.debug("GEMS RESHAPE_AND_CACHE")
+    dev = _lib.require_cuda(key, value, key_cache, value_cache, slot_mapping)
+    num_tokens = slot_mapping.size(0)
+    num_heads, head_size = key.size(1), key.size(2)
+    block_size, x = key_cache.size(3), key_cache.size(4)
+    if key.dtype != key_cache.dtype or value.dtype != value_cache.dtype or key.dtype != value.dtype:
+        raise RuntimeError("reshape_and_cache: key/value and the caches must share a dtype")
+    if not key_cache.is_contiguous() or not value_cache.is_contiguous():
+        raise RuntimeError("reshape_and_cache: the caches must be contiguous")
+    if key_cache.size(1) != num_heads or key_cache.size(2) * x != head_size or \
+            tuple(value_cache.shape[1:]) != (num_heads, head_size, block_size):
+        raise RuntimeError("reshape_and_cache: cache shapes do not match key/value")
+    if key.stride(2) != 1 or value.stride(2) != 1 or \
+            (num_heads > 1 and (key.stride(1) != head_size or value.stride(1) != head_size)):
+        raise RuntimeError("reshape_and_cache: key/value heads must be densely packed per token")
+    if slot_mapping.dtype != torch.int64:
+        slot_mapping = slot_mapping.to(torch.int64)
+    slot_mapping = slot_mapping.contiguous()
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().fg_reshape_and_cache(
+            key.data_ptr(), value.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+            slot_mapping.data_ptr(), num_tokens, num_heads, head_size, block_size, key_cache.size(0), x,
+            key.stride(0), value.stride(0), key.element_size(), _lib.stream_ptr(dev)))
     return None

@@ -18,7 +18,7 @@ from . import _lib
 
 logger = logging.getLogger("flag_gems." + __name__.split(".")[-1])
 
-__all__ = ["mm", "mm_out", "addmm", "addmm_out", "flash_attn_varlen_func", "flash_attention_forward", "rms_norm",
+__all__ = ["mm", "mm_out", "addmm", "addmm_out", "bmm", "flash_attn_varlen_func", "flash_attention_forward", "rms_norm",
            "get_higher_dtype"]
 
 _ordered_datatypes = [torch.float16, torch.bfloat16, torch.float32]
@@ -110,6 +110,43 @@ def mm_out(a, b, *, out):
         raise RuntimeError(f"mm_out: out has dtype {out.dtype}, expected {c_dtype}")
     logger.debug("GEMS MM_OUT, [shape info]: [-, %s, %s, %s](batch, M, N, K)", M, N, K)
     return _gemm(a, b, out)
+
+
+def bmm(A, B):
+    """``torch.bmm(A, B)`` with fp32 accumulation (aten::bmm override; ``src/flag_gems/ops/bmm.py:122-136``).
+    The batch is the third dimension of the GEMM kernel's tensor maps: one launch for all
+    problems.  Only the inner two dimensions are normalised (a matrix strided in both
+    dimensions is copied, as in ``mm``); the batch stride is passed as it is."""
+    logger.debug("GEMS BMM")
+    dev = _lib.require_cuda(A, B)
+    if A.dim() != 3 or B.dim() != 3:
+        raise RuntimeError("bmm: both arguments must be 3-D")
+    batch, M, K = A.shape
+    assert B.shape[0] == batch and B.shape[1] == K, "incompatible dimensions"
+    N = B.shape[2]
+    c_dtype = get_higher_dtype(A.dtype, B.dtype)
+    A = A.to(c_dtype) if A.dtype != c_dtype else A
+    B = B.to(c_dtype) if B.dtype != c_dtype else B
+    if (A.stride(1) > 1 and A.stride(2) > 1) or (batch > 1 and A.stride(0) == 0):
+        A = A.contiguous()
+    if (B.stride(1) > 1 and B.stride(2) > 1) or (batch > 1 and B.stride(0) == 0):
+        B = B.contiguous()
+    out = torch.empty((batch, M, N), dtype=c_dtype, device=A.device)
+    if batch == 0 or M == 0 or N == 0:
+        return out
+    p = _lib.GemmParams()
+    p.a, p.b, p.c = A.data_ptr(), B.data_ptr(), out.data_ptr()
+    p.bias = None
+    p.M, p.K, p.N = M, K, N
+    p.a_stride0, p.a_stride1 = A.stride(1), A.stride(2)
+    p.b_stride0, p.b_stride1 = B.stride(1), B.stride(2)
+    p.c_stride0, p.c_stride1 = out.stride(1), out.stride(2)
+    p.alpha, p.beta = 1.0, 0.0
+    p.dtype = _lib.dtype_code(c_dtype)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().fg_gemm_batched(C.byref(p), batch, A.stride(0), B.stride(0), out.stride(0), 0,
+                                               _lib.stream_ptr(dev)))
+    return out
 
 
 def _prep_addmm(bias, mat1, mat2):

@@ -22,6 +22,7 @@ __all__ = [
     "custom_gems_rms_forward_cuda",
     "custom_gems_rope_forward_cuda",
     "custom_gems_silu_and_mul",
+    "custom_gems_write_to_paged_cache",
     "custom_gems_flash_attention_impl_forward",
     "custom_silu_and_mul",
 ]
@@ -86,6 +87,13 @@ def custom_gems_silu_and_mul(self, x: torch.Tensor) -> torch.Tensor:
 
     d = x.shape[-1] // 2
     return gems_silu_and_mul(x[..., :d], x[..., d:])
+
+
+def custom_gems_write_to_paged_cache(key, value, key_cache, value_cache, slot_mapping, kv_cache_dtype, k_scale,
+                                     v_scale):
+    """``PagedAttention.write_to_paged_cache`` (vLLM v0 cache layout), patch_vllm_all.py:71-92."""
+    fused.reshape_and_cache(key, value, key_cache, value_cache, slot_mapping.flatten(), kv_cache_dtype, k_scale,
+                            v_scale)
 
 
 def custom_silu_and_mul(out: torch.Tensor, input: torch.Tensor):
@@ -181,6 +189,8 @@ def apply_gems_patches_to_vllm(verbose=True):
         ([("vllm.model_executor.layers.activation", "SiluAndMul")], "forward_cuda", custom_gems_silu_and_mul),
         ([("vllm.v1.attention.backends.flash_attn", "FlashAttentionImpl")], "forward",
          custom_gems_flash_attention_impl_forward),
+        ([("vllm.attention.ops.paged_attn", "PagedAttention")], "write_to_paged_cache",
+         custom_gems_write_to_paged_cache),
     ]
     for candidates, method, fn in targets:
         cls = _find(candidates)

@@ -102,6 +102,19 @@ FG_API int fg_gelu_and_mul(const void* a, const void* b, void* out, int ndim,
                            int dtype, void* stream);
 
 /* ------------------------------------------------------------------------
+ * reshape_and_cache: the same scatter into the vLLM v0 cache layout,
+ *   key_cache   [num_blocks, num_heads, head_size / x, block_size, x]
+ *   value_cache [num_blocks, num_heads, head_size, block_size]        (both contiguous).
+ * Replaces reshape_and_cache (src/flag_gems/fused/reshape_and_cache.py:14-106).
+ * key / value are [num_tokens, num_heads, head_size] with dense heads and the given
+ * token strides (elements); slots < 0 or beyond the cache are skipped; bit-exact copy.
+ * ---------------------------------------------------------------------- */
+FG_API int fg_reshape_and_cache(const void* key, const void* value, void* key_cache, void* value_cache,
+                                const int64_t* slot_mapping, int64_t num_tokens, int64_t num_heads,
+                                int64_t head_size, int64_t block_size, int64_t num_blocks, int64_t x,
+                                int64_t key_stride, int64_t value_stride, int elem_size, void* stream);
+
+/* ------------------------------------------------------------------------
  * rotary_embedding: rotate q [T, Hq, D] and k [T, Hk, D] by cos/sin rows.
  * Replaces flag_gems::rotary_embedding / rotary_embedding_inplace
  * (lib/rotary_embedding.cpp:96-280) and apply_rotary_pos_emb
@@ -179,6 +192,14 @@ typedef struct {
   int32_t reserved;
 } fg_gemm_params;
 FG_API int fg_gemm(const fg_gemm_params* p, void* stream);
+
+/* `batch` independent problems of the shape in `p` (bmm): problem i reads a + i * a_batch_stride,
+ * b + i * b_batch_stride, bias + i * bias_batch_stride and writes c + i * c_batch_stride (elements).
+ * Replaces bmm (src/flag_gems/ops/bmm.py:23-136).  One launch of the tensor-core kernel when the
+ * shape qualifies and the batch strides are multiples of 8 elements. */
+FG_API int fg_gemm_batched(const fg_gemm_params* p, int64_t batch, int64_t a_batch_stride,
+                           int64_t b_batch_stride, int64_t c_batch_stride, int64_t bias_batch_stride,
+                           void* stream);
 /* 1 if fg_gemm would take the tcgen05/TMA path for these arguments, 0 if the
  * generic path.  Pure host logic (no CUDA call). */
 FG_API int fg_gemm_uses_tcgen05(const fg_gemm_params* p);

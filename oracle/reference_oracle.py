@@ -162,6 +162,23 @@ def reshape_and_cache_flash(key: torch.Tensor, value: torch.Tensor, key_cache: t
         value_cache[blk[i], off[i], :, :] = value[i]
 
 
+def reshape_and_cache(key: torch.Tensor, value: torch.Tensor, key_cache: torch.Tensor,
+                      value_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """vLLM v0 layout, in place: ``key_cache[blk, :, :, off, :] = key[i].reshape(H, D/x, x)`` and
+    ``value_cache[blk, :, :, off] = value[i]`` (the loop of tests/test_attention_ops.py:1311-1321);
+    negative slots are skipped as in the kernel (src/flag_gems/fused/reshape_and_cache.py:30-32)."""
+    block_size = key_cache.shape[3]
+    reshaped_key = key.reshape(key.shape[0], *key_cache[0, :, :, 0, :].shape)
+    blk = torch.div(slot_mapping, block_size, rounding_mode="floor").tolist()
+    off = (slot_mapping % block_size).tolist()
+    slots = slot_mapping.tolist()
+    for i in range(slot_mapping.numel()):
+        if slots[i] < 0:
+            continue
+        key_cache[blk[i], :, :, off[i], :] = reshaped_key[i]
+        value_cache[blk[i], :, :, off[i]] = value[i]
+
+
 # --------------------------------------------------------------------------- norms
 def fused_add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
                        upcast: torch.dtype = torch.float64):
@@ -247,6 +264,11 @@ def gelu_and_mul(x: torch.Tensor, y: torch.Tensor, approximate: str = "none",
 def mm(a: torch.Tensor, b: torch.Tensor, upcast: torch.dtype = torch.float64) -> torch.Tensor:
     """``torch.mm`` on upcast inputs (tests/test_blas_ops.py:129-132)."""
     return torch.mm(a.to(upcast), b.to(upcast))
+
+
+def bmm(a: torch.Tensor, b: torch.Tensor, upcast: torch.dtype = torch.float64) -> torch.Tensor:
+    """``torch.bmm`` on upcast inputs (tests/test_blas_ops.py:95-111)."""
+    return torch.bmm(a.to(upcast), b.to(upcast))
 
 
 def addmm(bias, mat1, mat2, alpha=1.0, beta=1.0, upcast: torch.dtype = torch.float64) -> torch.Tensor:

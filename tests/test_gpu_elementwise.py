@@ -218,6 +218,29 @@ def test_reshape_and_cache_flash(fg, head_size, block_size, num_blocks, dtype):
     assert torch.equal(key_cache.cpu(), ref_k) and torch.equal(value_cache.cpu(), ref_v)  # bit-exact
 
 
+@pytest.mark.parametrize("head_size", [64, 80, 120, 256])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+@pytest.mark.parametrize("num_blocks", [128, 1000])
+@pytest.mark.parametrize("dtype", [torch.half, torch.bfloat16, torch.float])
+def test_reshape_and_cache_v0_layout(fg, head_size, block_size, num_blocks, dtype):
+    # tests/test_attention_ops.py:1254-1324: K cache [blocks, heads, D/x, block, x], V cache [blocks, heads, D, block]
+    random.seed(2025)
+    torch.manual_seed(2025)
+    num_tokens, num_heads = 42, 8
+    x = 16 // torch.tensor([], dtype=dtype).element_size()
+    slots = random.sample(range(num_blocks * block_size), num_tokens)
+    slots[5] = -1  # a padded token
+    slots = torch.tensor(slots, dtype=torch.long, device=DEV)
+    qkv = torch.randn(num_tokens, 3, num_heads, head_size, dtype=dtype, device=DEV)
+    _, key, value = qkv.unbind(dim=1)
+    key_cache = torch.randn(num_blocks, num_heads, head_size // x, block_size, x, dtype=dtype, device=DEV)
+    value_cache = torch.randn(num_blocks, num_heads, head_size, block_size, dtype=dtype, device=DEV)
+    ref_k, ref_v = key_cache.cpu().clone(), value_cache.cpu().clone()
+    O.reshape_and_cache(key.cpu(), value.cpu(), ref_k, ref_v, slots.cpu())
+    assert fg.reshape_and_cache(key, value, key_cache, value_cache, slots, "auto", None, None) is None
+    assert torch.equal(key_cache.cpu(), ref_k) and torch.equal(value_cache.cpu(), ref_v)  # bit-exact
+
+
 def test_reshape_and_cache_flash_edges(fg, golden_dir):
     c = torch.load(golden_dir / "golden_reshape_and_cache_flash.pt", weights_only=False)
     kc, vc = c["key_cache"].to(DEV), c["value_cache"].to(DEV)

@@ -144,3 +144,36 @@ def test_projection_shapes_linearity(fg, name):
     assert_close(cb[rows].cpu(), O.addmm(bias.cpu(), a[rows].cpu(), b.cpu()), torch.bfloat16, reduce_dim=K)
     # column-major B (the nn.Linear weight form) gives the same product
     assert_close(fg.mm(a, b.t().contiguous().t())[rows].cpu(), ref, torch.bfloat16, reduce_dim=K)
+
+
+# ---- bmm (aten::bmm override): the batch is the third dimension of the kernel's tensor maps
+@pytest.mark.parametrize("M,N,K", MNK_SHAPES + [(256, 512, 128), (1000, 520, 264)])
+@pytest.mark.parametrize("dtype", FLOAT_DTYPES)
+def test_bmm(fg, M, N, K, dtype):
+    # tests/test_blas_ops.py:95-111 (batch 4) plus shapes that take the tensor-core kernel
+    torch.manual_seed(0)
+    a = torch.randn((4, M, K), dtype=dtype, device=DEV)
+    b = torch.randn((4, K, N), dtype=dtype, device=DEV)
+    with fg.use_gems():
+        out = torch.bmm(a, b)
+    assert out.shape == (4, M, N) and out.dtype == dtype
+    assert_close(out.cpu(), O.bmm(a.cpu(), b.cpu()), dtype, reduce_dim=K)
+
+
+def test_bmm_layouts_and_batches(fg):
+    torch.manual_seed(1)
+    # transposed operands (column-major inner matrices), a broadcast batch and batch strides that
+    # are not the packed ones; batch 1 and batch 33; empty batch
+    a = torch.randn((6, 264, 384), dtype=torch.bfloat16, device=DEV)
+    b = torch.randn((6, 512, 264), dtype=torch.bfloat16, device=DEV)
+    out = fg.bmm(a.transpose(1, 2), b.transpose(1, 2))          # [6, 384, 264] x [6, 264, 512]
+    assert_close(out.cpu(), O.bmm(a.transpose(1, 2).cpu(), b.transpose(1, 2).cpu()), torch.bfloat16, reduce_dim=264)
+    w = torch.randn((264, 512), dtype=torch.bfloat16, device=DEV)
+    out = fg.bmm(a.transpose(1, 2), w.expand(6, 264, 512))     # shared right operand
+    assert_close(out.cpu(), O.bmm(a.transpose(1, 2).cpu(), w.expand(6, 264, 512).cpu()), torch.bfloat16, reduce_dim=264)
+    big = torch.randn((33, 2, 128, 256), dtype=torch.float16, device=DEV)
+    x, y = big[:, 0], big[:, 1].transpose(1, 2)                # batch stride 2 * 128 * 256
+    assert_close(fg.bmm(x, y).cpu(), O.bmm(x.cpu(), y.cpu()), torch.float16, reduce_dim=256)
+    assert_close(fg.bmm(x[:1], y[:1]).cpu(), O.bmm(x[:1].cpu(), y[:1].cpu()), torch.float16, reduce_dim=256)
+    assert fg.bmm(x[:0], y[:0]).shape == (0, 128, 128)
+    assert _lib.device_status() == 0

@@ -33,14 +33,14 @@ def test_enable_and_use_gems_surface(tmp_path):
     lib = _FakeLib()
     log = tmp_path / "oplist.log"
     fg.enable(lib=lib, unused=["addmm_out"], record=True, once=True, path=str(log))
-    assert fg.all_ops() == ["addmm", "mm", "mm.out", "_flash_attention_forward"]
+    assert fg.all_ops() == ["addmm", "mm", "mm.out", "bmm", "_flash_attention_forward"]
     logging.getLogger("flag_gems.ops").debug("GEMS TEST RECORD")
     fg.logging_utils.teardown_flaggems_logging()
     assert "GEMS TEST RECORD" in log.read_text()
     # the scoped form registers on a private Library and destroys it on exit; CPU
     # tensors are untouched by CUDA-key overrides
     with fg.use_gems():
-        assert set(fg.all_ops()) == {"mm", "mm.out", "addmm", "addmm.out", "_flash_attention_forward"}
+        assert set(fg.all_ops()) == {"mm", "mm.out", "addmm", "addmm.out", "bmm", "_flash_attention_forward"}
         a = torch.randn(3, 4)
         torch.testing.assert_close(torch.mm(a, a.t()), a @ a.t())
     for name in ("flash_attn_varlen_func", "reshape_and_cache_flash", "fused_add_rms_norm", "apply_rotary_pos_emb",
