@@ -56,19 +56,47 @@ def load_peaks():
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the clock-event (throttle) reasons while the timed region runs:
+    an NVML polling thread (every ~5 ms, read-only queries), or `nvidia-smi -lms` when the
+    NVML bindings are missing.  The timed region of the default run is only ~50 ms long, too
+    short for nvidia-smi's own sampling loop to be sure to hit it."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.lines = []      # nvidia-smi form: (time, csv line)
+        self.samples = []    # NVML form: (time, sm_mhz, reason names)
         self.thread = None
+        self.stop_flag = False
+        self.smax = None
+        self.nvml = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            pr = torch.cuda.get_device_properties(self.index)
+            bus = "%08x:%02x:%02x.0" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+            h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        except Exception:  # noqa: BLE001
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+        return pynvml, h
 
     def start(self):
+        try:
+            self.nvml, self.handle = self._nvml_handle()
+            self.smax = float(self.nvml.nvmlDeviceGetMaxClockInfo(self.handle, self.nvml.NVML_CLOCK_SM))
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
@@ -79,21 +107,48 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._read, daemon=True)
         self.thread.start()
 
+    def _poll(self):
+        n = self.nvml
+        get_reasons = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(n, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        bits = {
+            "hw_slowdown": getattr(n, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(n, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self.stop_flag:
+            try:
+                clk = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = int(get_reasons(self.handle))
+                self.samples.append((time.time(), clk, [k for k, b in bits.items() if mask & b]))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.004)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
     def stop(self, t0: float, t1: float):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=1)
+            inside = [x for x in self.samples if t0 <= x[0] <= t1] or \
+                [x for x in self.samples if t0 - 0.05 <= x[0] <= t1 + 0.05] or self.samples
+            sm = [x[1] for x in inside]
+            reasons = sorted({r for x in inside for r in x[2]})
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.smax, "reasons": reasons,
+                    "samples": len(sm), "source": "nvml"}
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML bindings and no nvidia-smi"], "samples": 0}
+        time.sleep(0.25)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
         except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, smax, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ts, line in self.lines:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 8:
@@ -103,15 +158,15 @@ class ClockSampler:
             except ValueError:
                 continue
             smax = mx
-            if t0 - 0.05 <= ts <= t1 + 0.15:
+            if t0 - 0.05 <= ts <= t1 + 0.25:
                 sm.append(clk)
-                for n, v in zip(names, parts[4:8]):
+                for n, v in zip(self.NAMES, parts[4:8]):
                     if v.lower().startswith("active"):
                         reasons.add(n)
         if not sm:  # region shorter than one sample: use whatever was seen
             sm = [float(l.split(",")[0]) for _, l in self.lines if l and l[0].isdigit()]
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- workload
