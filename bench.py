@@ -181,6 +181,7 @@ class Step:
 
         self.gather = gather
         self.row_blocks = row_blocks
+        self.skip_gather = False   # N > 1: second timing of the step without the all-gathers
 
         self.fg, self.W, self.fdist = fg, W, fdist
         self.device, self.rank, self.world = device, rank, world
@@ -293,7 +294,7 @@ class Step:
                     fg.addmm_out(bias, a[r0:r1], b, out=c[r0:r1])
                 else:
                     fg.mm_out(a[r0:r1], b, out=c[r0:r1])
-                if self.world > 1:
+                if self.world > 1 and not self.skip_gather:
                     # column-parallel: gather the shards on the side stream; the next operators
                     # of the step overlap with the transfer, the step ends when all gathers have landed
                     self.comm_stream.wait_stream(cur)
@@ -321,7 +322,7 @@ class Step:
                 events[i][1].record()
             if after is not None:
                 after(i)
-        if self.comm_stream is not None:
+        if self.comm_stream is not None and not self.skip_gather:
             if self.gather != "nccl":
                 with torch.cuda.stream(self.comm_stream):
                     next(iter(self.gemm.values()))[4].finish()  # one tiny all-reduce closes all pushes
@@ -826,6 +827,25 @@ def main():
         out["cpu_baseline"] = {"value": n / t, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                                "sample": sample, "step_seconds_scaled": t}
     if world > 1:
+        # the same K steps without the all-gathers: what the sharded operators alone scale like
+        step.skip_gather = True
+        for _ in range(2):
+            step.run()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        g0.record()
+        for _ in range(args.steps):
+            step.run()
+        g1.record()
+        barrier()
+        step.skip_gather = False
+        ms_ng = g0.elapsed_time(g1)
+        t = torch.tensor([ms_ng], device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms_ng = float(t.item())
+        out["no_gather"] = {"value": world * n_ops / (ms_ng / args.steps * 1e-3), "unit": UNIT,
+                            "ms_per_step": ms_ng / args.steps,
+                            "note": "same step with the projection outputs left sharded (no NVLink traffic)"}
         gathers = []
         for name, (g0, g1) in step.comm_events.items():
             ms = g0.elapsed_time(g1)
