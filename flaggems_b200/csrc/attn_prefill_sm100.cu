@@ -1,6 +1,6 @@
 // Prefill attention for head dim 128 on sm_100a tensor cores (tcgen05 + TMEM).
 //
-// One CTA = 128 query positions of one sequence x TWO query heads of the same KV
+// One work item = 128 query positions of one sequence x TWO query heads of the same KV
 // group (one when the group size is odd): the two 128-row Q tiles share every K/V
 // tile, which halves the K/V traffic and lets the tensor pipe work on one tile while
 // the softmax warps work on the other.
@@ -28,6 +28,9 @@
 // P aliases the first 32 columns of its score buffer (keys [16k,16k+16) in columns 8k..8k+8).
 // Every wait in the kernel is an mbarrier wait with a time limit (no named barriers, no
 // register reallocation): a wait that gives up sets the device status word and the CTA drains.
+// The kernel is persistent: one CTA per SM keeps its shared memory, TMEM and tensor maps and
+// draws work items from a ticket counter (query blocks of a sequence from the longest causal
+// prefix to the shortest); between items the CTA synchronises and re-initialises its barriers.
 //
 // Measured costs that shaped this layout (B200, SM clocks, microbenchmarks on an otherwise
 // idle SM): an mbarrier arrive reaches a waiting thread after 110-150; the first result of
@@ -42,6 +45,8 @@
 // Covers: fp16/bf16, head dim 128, causal or full attention, paged (block size a
 // power of two >= 8) or contiguous KV.  ALiBi, soft-cap, windows and other head dims
 // take the general kernel.
+#include <atomic>
+
 #include "attn_common.cuh"
 #include "sm100_common.cuh"
 
@@ -65,6 +70,10 @@ extern "C" __attribute__((visibility("default"))) int fg_debug_read_trace(long l
 
 namespace fg {
 
+// Ticket counters of the persistent prefill kernel (one per launch in flight, see the launcher).
+constexpr unsigned int kTicketRing = 64;
+__device__ unsigned int g_prefill_tickets[kTicketRing];
+
 int* device_status_ptr();
 
 namespace {
@@ -85,6 +94,9 @@ struct PrefillArgs {
   int page_rows;        // rows fetched per TMA box for K/V (min(block_size, 128)); 128 when contiguous
   int pages_per_tile;   // 128 / page_rows
   int is_bf16;
+  int num_mb, num_hp;          // work items: (query block, head pair, sequence), query block fastest
+  int64_t num_items;
+  unsigned int* ticket;        // next work item of this launch (zeroed on the stream before the launch)
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -116,52 +128,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                             const __grid_constant__ CUtensorMap tmap_v, PrefillArgs pa) {
   using namespace sm100;
   const AttnArgs& a = pa.a;
-  const int num_mb = gridDim.x;
-  const int m_block = num_mb - 1 - blockIdx.x;
-  const int b = blockIdx.z;
   const int NT = pa.tiles;
-  const int h0 = blockIdx.y * NT;
-  const SeqInfo s = seq_info(a, b);
-  const int m0 = m_block * BM;
-  if (m0 >= s.q_len) return;  // before any allocation
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // A wait that timed out anywhere on this device left the status word set: finish the
   // launch quickly instead of letting every remaining CTA run into the same timeout
   // (one thread reads it so that the whole CTA takes the same decision).
   __shared__ int s_drain;
+  __shared__ int64_t s_item;
   if (threadIdx.x == 0) s_drain = *reinterpret_cast<volatile int*>(a.status);
   __syncthreads();
   if (s_drain != 0) return;
-
-  const int shift = s.k_len - s.q_len;
-  int vis = s.k_len;                  // keys visible to at least one row of this block
-  if (a.causal) vis = max(0, min(vis, m0 + BM + shift));
-  const int n_steps = (vis + STEP - 1) / STEP;
-  const int n_tiles = (n_steps + 1) / 2;   // K/V tiles of 128 keys
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef FG_PREFILL_TRACE
-  const bool trace_on = (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) && (lane == 0);
-#endif
-
-  if (n_tiles == 0) {
-    // no visible key for any row of the block: zeros, lse = +inf
-    for (int idx = threadIdx.x; idx < NT * BM * (HD / 8); idx += NUM_THREADS) {
-      const int t = idx / (BM * (HD / 8));
-      const int r = (idx / (HD / 8)) % BM;
-      const int c = idx % (HD / 8);
-      if (m0 + r < s.q_len) {
-        uint4 z = make_uint4(0, 0, 0, 0);
-        char* o = reinterpret_cast<char*>(a.out) +
-                  ((int64_t)(s.q_begin + m0 + r) * a.o_rs + (int64_t)(h0 + t) * a.o_hs) * 2 + c * 16;
-        *reinterpret_cast<uint4*>(o) = z;
-      }
-    }
-    if (a.lse)
-      for (int idx = threadIdx.x; idx < NT * BM; idx += NUM_THREADS) {
-        const int t = idx / BM, r = idx % BM;
-        if (m0 + r < s.q_len) a.lse[(int64_t)(h0 + t) * a.total_q + s.q_begin + m0 + r] = INFINITY;
-      }
-    return;
-  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -182,18 +158,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], NT);   // one commit per issuing thread
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], NT);
-    }
-    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
-    for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
-    for (int i = 0; i < 4; ++i) mbar_init(&o_done[i], 1);
     *abort_flag = 0;
-    mbar_fence_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
@@ -206,8 +171,71 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Register budget: 640 threads start with 96 registers each; the control warpgroup hands
-  // most of its share to the four softmax warpgroups, which keep 64 scores per thread live.
+  // ---- persistent loop: a CTA keeps its shared memory, TMEM and tensor maps and draws work items
+  // (query block x head pair x sequence; the heaviest query blocks of a sequence first) from a
+  // ticket counter.  Blocks beyond a sequence's end cost one counter increment instead of a CTA
+  // launch, and launch, allocation and descriptor fetch are paid once per SM, not once per item.
+  int n_done = 0;
+  for (;;) {
+    if (threadIdx.x == 0) s_item = (int64_t)atomicAdd(pa.ticket, 1u);
+    __syncthreads();
+    const int64_t item = s_item;
+    if (item >= pa.num_items) break;
+    const int m_block = pa.num_mb - 1 - (int)(item % pa.num_mb);
+    const int h0 = (int)((item / pa.num_mb) % pa.num_hp) * NT;
+    const int b = (int)(item / ((int64_t)pa.num_mb * pa.num_hp));
+    const SeqInfo s = seq_info(a, b);
+    const int m0 = m_block * BM;
+    if (m0 >= s.q_len) {
+      __syncthreads();   // everybody has read s_item
+      continue;
+    }
+    const int shift = s.k_len - s.q_len;
+    int vis = s.k_len;                  // keys visible to at least one row of this block
+    if (a.causal) vis = max(0, min(vis, m0 + BM + shift));
+    const int n_steps = (vis + STEP - 1) / STEP;
+    const int n_tiles = (n_steps + 1) / 2;   // K/V tiles of 128 keys
+#ifdef FG_PREFILL_TRACE
+    const bool trace_on = (item == 0) && (lane == 0);
+#endif
+  if (n_tiles == 0) {
+    // no visible key for any row of the block: zeros, lse = +inf
+    for (int idx = threadIdx.x; idx < NT * BM * (HD / 8); idx += NUM_THREADS) {
+      const int t = idx / (BM * (HD / 8));
+      const int r = (idx / (HD / 8)) % BM;
+      const int c = idx % (HD / 8);
+      if (m0 + r < s.q_len) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        char* o = reinterpret_cast<char*>(a.out) +
+                  ((int64_t)(s.q_begin + m0 + r) * a.o_rs + (int64_t)(h0 + t) * a.o_hs) * 2 + c * 16;
+        *reinterpret_cast<uint4*>(o) = z;
+      }
+    }
+    if (a.lse)
+      for (int idx = threadIdx.x; idx < NT * BM; idx += NUM_THREADS) {
+        const int t = idx / BM, r = idx % BM;
+        if (m0 + r < s.q_len) a.lse[(int64_t)(h0 + t) * a.total_q + s.q_begin + m0 + r] = INFINITY;
+      }
+    __syncthreads();
+    continue;
+  }
+
+  if (threadIdx.x == 0) {
+    if (n_done > 0)
+      for (int i = 0; i < 21; ++i) mbar_inval(&bars[i]);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], NT);   // one commit per issuing thread
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], NT);
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
+    for (int i = 0; i < 4; ++i) mbar_init(&o_done[i], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
   const int hk = h0 / a.group;
   const int st_code = kStatusAttnTimeout;
   // Every wait of a warp is polled by lane 0 and its outcome broadcast, so that a wait
@@ -465,6 +493,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     }
   }
 
+    // ---- end of the item: every role has left its loop, every MMA and copy has been waited for
+    tc_fence_before();
+    __syncthreads();
+    ++n_done;
+    if (*abort_flag) break;
+  }
+
   // ================================ teardown ======================================
   tc_fence_before();
   __syncthreads();
@@ -535,6 +570,7 @@ int attn_prefill_sm100(const AttnArgs& a, int dtype, cudaStream_t st) {
     if (rc != FG_OK) return rc;
   }
   static thread_local int attr_dev = -1;
+  static thread_local unsigned int* tickets = nullptr;
   int dev = 0;
   cudaGetDevice(&dev);
   if (attr_dev != dev) {
@@ -542,9 +578,23 @@ int attn_prefill_sm100(const AttnArgs& a, int dtype, cudaStream_t st) {
                                     SMEM_BYTES));
     FG_CUDA_OK(cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES));
+    void* sym = nullptr;
+    FG_CUDA_OK(cudaGetSymbolAddress(&sym, g_prefill_tickets));
+    tickets = reinterpret_cast<unsigned int*>(sym);
     attr_dev = dev;
   }
-  dim3 grid((a.max_q + BM - 1) / BM, a.H / pa.tiles, a.batch);
+  pa.num_mb = (int)((a.max_q + BM - 1) / BM);
+  pa.num_hp = a.H / pa.tiles;
+  pa.num_items = (int64_t)pa.num_mb * pa.num_hp * a.batch;
+  if (pa.num_items <= 0) return FG_OK;
+  if (pa.num_items >= 4000000000LL) return fail(FG_ERR_TOO_LARGE, "flash_attn_varlen: too many query blocks");
+  // One ticket counter per launch, taken round-robin from a small ring so that launches in
+  // flight on different streams do not share one; zeroed on the stream ahead of the kernel.
+  static std::atomic<unsigned int> launch_seq{0};
+  pa.ticket = tickets + (launch_seq.fetch_add(1, std::memory_order_relaxed) % kTicketRing);
+  FG_CUDA_OK(cudaMemsetAsync(pa.ticket, 0, sizeof(unsigned int), st));
+  const int64_t ctas = pa.num_items < num_sms() ? pa.num_items : num_sms();
+  dim3 grid((unsigned)ctas);
   if (pa.is_bf16)
     attn_prefill_tcgen05_kernel<true><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tq, tk, tv, pa);
   else
