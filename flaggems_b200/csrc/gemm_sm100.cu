@@ -1,17 +1,24 @@
 // Dense GEMM for the mm/addmm projections on sm_100a:
 //   C[M,N] = alpha * A[M,K] @ B[K,N] (+ beta * bias), 16-bit inputs, fp32 accumulate.
 //
-// Persistent kernel, one CTA per SM, 128x256 output tile, BK = 64:
-//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A and B into a 4-stage
-//               128-byte-swizzled shared-memory ring (48 KB per stage)
-//   warp 1      allocates TMEM and issues tcgen05.mma (M128 N256 K16) from one thread;
-//               two 256-column fp32 accumulators so tile i+1 overlaps the epilogue of i
-//   warps 2-5   epilogue: tcgen05.ld the accumulator, alpha/beta/bias in fp32, round
-//               once, 16-byte stores
+// Persistent kernel, one CTA per SM, BK = 64, two tile shapes (template parameter MT):
+//   MT = 1: 128x256 output tile, 4-stage ring of 48 KB stages, two 256-column fp32
+//           accumulators in TMEM so that tile i+1's main loop overlaps the epilogue of tile i;
+//   MT = 2: 256x256 output tile as two M128 MMAs per K step that share the B operand,
+//           3-stage ring of 64 KB stages, the two accumulators fill TMEM (no overlap of the
+//           epilogue).  A third less operand traffic from L2 per flop and a deeper ring in
+//           clocks; taken for K-major A when the wave count does not eat the gain.
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A and B into the
+//               128-byte-swizzled shared-memory ring
+//   warp 1      allocates TMEM and issues tcgen05.mma (M128 N256 K16) from one thread
+//   warps 2-9   epilogue (two warps per TMEM lane quarter, 128 columns each): tcgen05.ld the
+//               accumulator, alpha/beta/bias in fp32, round once, 16-byte stores
 // Both operands may be row- or column-major; the UMMA descriptors carry the
 // majorness, the TMA boxes differ (one [64 x rows] box for a K-major operand, one
 // [64 x 64] box per 64 rows for an MN-major operand).  M, N and K tails are handled
 // by TMA zero fill on loads and predication on stores.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100_common.cuh"
 
@@ -21,12 +28,18 @@ int* device_status_ptr();
 
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
-constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KB
+constexpr int BM = 128, BN = 256, BK = 64;   // BM: rows of one MMA; a tile has MT * BM rows
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-constexpr int NUM_THREADS = 192;
+constexpr int MAX_STAGES = 4;
+template <int MT>
+struct Cfg {
+  static constexpr int TILE_M = MT * BM;
+  static constexpr int STAGES = MT == 1 ? 4 : 3;
+  static constexpr int A_STAGE_BYTES = TILE_M * BK * 2;  // 16 / 32 KB
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+};
+constexpr int SMEM_BYTES = 4 * (BM * BK * 2 + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;  // both shapes: 192 KB
+constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int TMEM_COLS = 512;
 
 struct GemmArgs {
@@ -41,6 +54,7 @@ struct GemmArgs {
   int is_bf16;
   int group_m;
   int c_vec_ok;                // 16-byte stores legal for C
+  int bias_vec;                // bias is one contiguous, 16-byte aligned row shared by all rows
   int64_t batch;               // independent problems sharing the shape (bmm); the tensor maps carry
   int64_t c_bs, bias_bs;       // the batch as their third dimension, C and bias by these strides
   int* status;
@@ -72,17 +86,19 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
   tn = r / rows;
 }
 
-template <typename T>
+template <typename T, int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     GemmArgs g) {
   using namespace sm100;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* bars_base = smem + STAGES * STAGE_BYTES;
+  constexpr int STAGES = Cfg<MT>::STAGES, STAGE_BYTES = Cfg<MT>::STAGE_BYTES;
+  constexpr int A_STAGE_BYTES = Cfg<MT>::A_STAGE_BYTES, TILE_M = Cfg<MT>::TILE_M;
+  uint8_t* bars_base = smem + 4 * (BM * BK * 2 + B_STAGE_BYTES);
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(bars_base);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* acc_full = empty_bar + STAGES;   // [2]
+  uint64_t* empty_bar = full_bar + MAX_STAGES;
+  uint64_t* acc_full = empty_bar + MAX_STAGES;   // [2]
   uint64_t* acc_empty = acc_full + 2;        // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -96,7 +112,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   __syncthreads();
   if (s_drain != 0) return;
 
-  const int64_t tiles_m = (g.M + BM - 1) / BM;
+  const int64_t tiles_m = (g.M + TILE_M - 1) / TILE_M;
   const int64_t tiles_n = (g.N + BN - 1) / BN;
   const int64_t tiles_per_batch = tiles_m * tiles_n;
   const int64_t num_tiles = tiles_per_batch * g.batch;
@@ -109,7 +125,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 128);
+      mbar_init(&acc_empty[b], 256);   // every epilogue thread arrives
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -135,7 +151,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         int64_t tm, tn;
         const int bi = (int)(tile / tiles_per_batch);
         tile_coords(tile - bi * tiles_per_batch, tiles_m, tiles_n, g.group_m, tm, tn);
-        const int m0 = (int)(tm * BM), n0 = (int)(tn * BN);
+        const int m0 = (int)(tm * TILE_M), n0 = (int)(tn * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, kStatusGemmTimeout)) {
             ok = false;
@@ -149,7 +165,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, m0, bi);
           } else {
 #pragma unroll
-            for (int b = 0; b < BM / 64; ++b)
+            for (int b = 0; b < TILE_M / 64; ++b)
               tma_load_3d(sa + b * (64 * BK * 2), &tmap_a, &full_bar[stage], m0 + 64 * b, k0, bi);
           }
           if (!g.b_mn_major) {
@@ -179,8 +195,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int64_t local = 0;
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
-        const int buf = (int)(local & 1);
-        const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+        // MT = 1: two accumulators, used alternately.  MT = 2: both halves of TMEM hold this tile.
+        const int buf = MT == 1 ? (int)(local & 1) : 0;
+        const uint32_t acc_phase = MT == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, g.status, kStatusGemmTimeout)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
@@ -194,9 +211,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = umma_desc_sw128(sa + k * a_kstep, a_lbo, 1024);
             const uint64_t bdesc = umma_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
-            mma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              // rows mt*128.. of the A stage: 128 rows x 128 B further on (K-major A only for MT = 2)
+              const uint64_t adesc = umma_desc_sw128(sa + mt * (BM * BK * 2) + k * a_kstep, a_lbo, 1024);
+              mma_f16_ss(d_tmem + (uint32_t)(mt * BN), adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           tc_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == STAGES) {
@@ -209,23 +230,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int quarter = warp & 3;          // TMEM lane quarter this warp may read
+    const int chalf = (warp - 2) >> 2;     // two warps share a quarter: columns [0,128) and [128,256) of the tile
     int64_t local = 0;
     for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
-      const int buf = (int)(local & 1);
-      const uint32_t acc_phase = (uint32_t)((local >> 1) & 1);
+      const int buf = MT == 1 ? (int)(local & 1) : 0;
+      const uint32_t acc_phase = MT == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
       int64_t tm, tn;
       const int64_t bi = tile / tiles_per_batch;
       tile_coords(tile - bi * tiles_per_batch, tiles_m, tiles_n, g.group_m, tm, tn);
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, g.status, kStatusGemmTimeout)) break;
       tc_fence_after();
-      const int64_t row = tm * BM + quarter * 32 + lane;
       const int64_t col0 = tn * BN;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-      T* crow = reinterpret_cast<T*>(g.c) + bi * g.c_bs + row * g.c_s0;
       const T* bias = reinterpret_cast<const T*>(g.bias) + bi * g.bias_bs;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int mt = 0; mt < MT; ++mt) {
+      const int64_t row = tm * TILE_M + mt * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf + mt) * BN);
+      T* crow = reinterpret_cast<T*>(g.c) + bi * g.c_bs + row * g.c_s0;
+#pragma unroll 1
+      for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(taddr + c * 32, r);
         tmem_ld_wait();
@@ -235,11 +259,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           if (g.has_bias) {
+            if (g.bias_vec && col + 32 <= g.N) {
+              // the usual addmm bias, a row vector: four 16-byte loads (the same addresses in
+              // every lane) instead of 32 strided scalar ones
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int64_t cj = col + j;
-              const float bv = cj < g.N ? Cvt<T>::to_f32(bias[row * g.bias_s0 + cj * g.bias_s1]) : 0.f;
-              v[j] = v[j] * g.alpha + bv * g.beta;
+              for (int q = 0; q < 4; ++q) {
+                float bv[8];
+                Vec16<T>::unpack(ldg16(bias + col + q * 8), bv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[q * 8 + j] = fmaf(v[q * 8 + j], g.alpha, bv[j] * g.beta);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int64_t cj = col + j;
+                const float bv = cj < g.N ? Cvt<T>::to_f32(bias[row * g.bias_s0 + cj * g.bias_s1]) : 0.f;
+                v[j] = v[j] * g.alpha + bv * g.beta;
+              }
             }
           }
           if (g.c_vec_ok && col + 32 <= g.N) {
@@ -258,6 +294,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               if (col + j < g.N) crow[col + j] = Cvt<T>::from_f32(v[j]);
           }
         }
+      }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);
@@ -281,6 +318,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 }  // namespace
 
+// Cost of a 256x256 tile relative to two 128x256 tiles (tile-shape choice below).
+constexpr double kBigTileCost = 0.85;
+// 0: choose; 1 / 2: force the tile shape (set from the environment variable FLAGGEMS_B200_GEMM_MT,
+// for measurements).
+static const int g_force_mt = []() {
+  const char* e = getenv("FLAGGEMS_B200_GEMM_MT");
+  return e ? atoi(e) : 0;
+}();
+
 static bool tcgen05_eligible(const fg_gemm_params* p) {
   if (p->dtype != FG_BF16 && p->dtype != FG_F16) return false;
   if (p->M < 1 || p->N < 1 || p->K < 1) return false;
@@ -302,6 +348,21 @@ static bool tcgen05_eligible(const fg_gemm_params* p) {
   return true;
 }
 
+template <typename T, int MT>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int grid, cudaStream_t st) {
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (attr_dev != dev) {
+    FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<T, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES));
+    attr_dev = dev;
+  }
+  gemm_tcgen05_kernel<T, MT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, g);
+  FG_CHECK_LAUNCH("gemm_tcgen05_kernel");
+  return FG_OK;
+}
+
 int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) {
   using namespace fg;
   // A: K-major if a_stride1 == 1 (row-major), else M-major.  Degenerate shapes with
@@ -309,6 +370,20 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
   const bool a_mn = !(p->a_stride1 == 1 && p->a_stride0 % 8 == 0 && p->a_stride0 >= p->K);
   // B [K,N]: K-major if b_stride0 == 1 (column-major storage), else N-major.
   const bool b_mn = !(p->b_stride0 == 1 && p->b_stride1 % 8 == 0 && p->b_stride1 >= p->K);
+
+  // Tile shape: 256x256 needs a third less operand traffic per flop but has half as many,
+  // twice as long tiles; it is taken when its last, partly filled wave costs less than that
+  // gains, for K-major A only.  Measured at M = 8192 (bf16, B200): 1461 against 1392 TFLOP/s
+  // for N = 28672, K = 4096 with bias, 1504 against 1356 for N = 4096, K = 14336, a tie for
+  // N = 6144 where the big tile's sixth wave is a fifth full.
+  const int sms = sm_budget();
+  const int64_t tn = (p->N + BN - 1) / BN;
+  const int64_t tiles1 = ((p->M + BM - 1) / BM) * tn * bt.batch;
+  const int64_t tiles2 = ((p->M + 2 * BM - 1) / (2 * BM)) * tn * bt.batch;
+  const int64_t waves1 = (tiles1 + sms - 1) / sms, waves2 = (tiles2 + sms - 1) / sms;
+  int mt = (!a_mn && p->M > BM && (double)waves2 * 2.0 * kBigTileCost < (double)waves1) ? 2 : 1;
+  if (g_force_mt == 1 || (g_force_mt == 2 && !a_mn)) mt = g_force_mt;
+  const int tile_m = mt * BM;
 
   CUtensorMap ta, tb;
   {
@@ -319,7 +394,7 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
     box[2] = 1;
     if (!a_mn) {
       dims[0] = (uint64_t)p->K; dims[1] = (uint64_t)p->M; strides[0] = (uint64_t)p->a_stride0 * 2;
-      box[0] = 64; box[1] = BM;
+      box[0] = 64; box[1] = (uint32_t)tile_m;
     } else {
       dims[0] = (uint64_t)p->M; dims[1] = (uint64_t)p->K; strides[0] = (uint64_t)p->a_stride1 * 2;
       box[0] = 64; box[1] = BK;
@@ -348,50 +423,28 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
   g.a_mn_major = a_mn; g.b_mn_major = b_mn;
   g.is_bf16 = p->dtype == FG_BF16;
   // Row tiles per sweep over the column tiles: as many as keep the A panel of a group
-  // (group_m x 128 rows x K) around 32 MB, so that it stays L2-resident while B streams
-  // through once per group instead of once per 8 row tiles.
+  // (group_m x tile rows x K) around 32 MB, so that it stays L2-resident while B streams
+  // through once per group instead of once per few row tiles.
   {
-    const int64_t panel = (int64_t)BM * p->K * 2;
+    const int64_t panel = (int64_t)tile_m * p->K * 2;
     int64_t gm = (32ll << 20) / (panel > 0 ? panel : 1);
     if (gm < 4) gm = 4;
     if (gm > 64) gm = 64;
     g.group_m = (int)gm;
   }
   g.c_vec_ok = aligned16(p->c) && (p->c_stride0 % 8 == 0) && (bt.batch == 1 || bt.c_bs % 8 == 0);
+  g.bias_vec = p->bias != nullptr && p->bias_stride0 == 0 && p->bias_stride1 == 1 && aligned16(p->bias) &&
+               (bt.batch == 1 || bt.bias_bs % 8 == 0);
   g.batch = bt.batch; g.c_bs = bt.c_bs; g.bias_bs = bt.bias_bs;
   g.status = device_status_ptr();
   if (!g.status) return fail(FG_ERR_CUDA, "gemm: device status word unavailable");
 
-  const int64_t tiles = ((p->M + BM - 1) / BM) * ((p->N + BN - 1) / BN) * bt.batch;
-  int grid = sm_budget();  // persistent: one CTA per SM it may use
+  const int64_t tiles = mt == 2 ? tiles2 : tiles1;
+  int grid = sms;  // persistent: one CTA per SM it may use
   if (tiles < grid) grid = (int)tiles;
-  if (p->dtype == FG_BF16) {
-    static thread_local int attr_dev = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (attr_dev != dev) {
-      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_dev = dev;
-    }
-    gemm_tcgen05_kernel<__nv_bfloat16><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, g);
-  } else {
-    static thread_local int attr_dev = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (attr_dev != dev) {
-      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__nv_bfloat16>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      FG_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<__half>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_dev = dev;
-    }
-    gemm_tcgen05_kernel<__half><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, g);
-  }
-  FG_CHECK_LAUNCH("gemm_tcgen05_kernel");
-  return FG_OK;
+  if (p->dtype == FG_BF16)
+    return mt == 2 ? launch_gemm<__nv_bfloat16, 2>(ta, tb, g, grid, st) : launch_gemm<__nv_bfloat16, 1>(ta, tb, g, grid, st);
+  return mt == 2 ? launch_gemm<__half, 2>(ta, tb, g, grid, st) : launch_gemm<__half, 1>(ta, tb, g, grid, st);
 }
 
 bool gemm_tcgen05_eligible(const fg_gemm_params* p) { return tcgen05_eligible(p); }
