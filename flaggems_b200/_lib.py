@@ -73,6 +73,23 @@ class AttnParams(C.Structure):
     )
 
 
+class SchedulerParams(C.Structure):
+    _fields_ = (
+        [(n, C.c_int32) for n in (
+            "batch_size", "max_seqlen_q", "max_seqlen_k", "num_heads", "num_heads_k", "headdim", "headdim_v",
+            "elem_size", "page_size", "max_seqlen_k_new", "is_causal", "window_size_left", "window_size_right",
+            "has_softcap", "num_splits", "pack_gqa", "sm_margin", "arch", "num_sm", "varlen_q", "has_leftpad")]
+        + [(n, C.c_void_p) for n in (
+            "seqused_k", "cu_seqlens_q", "cu_seqlens_k", "cu_seqlens_k_new", "seqused_q", "leftpad_k")]
+    )
+
+
+class SchedulerPlan(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "num_splits", "pack_gqa", "block_m", "block_n", "use_dynamic_split", "is_causal", "is_local",
+        "q_per_kv", "heads", "metadata_len")]
+
+
 _I64 = C.c_int64
 _P = C.c_void_p
 _PI64 = C.POINTER(C.c_int64)
@@ -100,6 +117,8 @@ SIGNATURES = {
     "fg_flash_attn_path": (C.c_int, [C.POINTER(AttnParams)]),
     "fg_flash_attn_decode_static": (C.c_int, [C.POINTER(AttnParams), _P]),
     "fg_flash_attn_decode_static_capacity": (C.c_int64, []),
+    "fg_scheduler_plan": (C.c_int, [C.POINTER(SchedulerParams), C.POINTER(SchedulerPlan)]),
+    "fg_get_scheduler_metadata": (C.c_int, [C.POINTER(SchedulerParams), _P, _P]),
 }
 
 

@@ -57,8 +57,25 @@ struct GemmArgs {
   int bias_vec;                // bias is one contiguous, 16-byte aligned row shared by all rows
   int64_t batch;               // independent problems sharing the shape (bmm); the tensor maps carry
   int64_t c_bs, bias_bs;       // the batch as their third dimension, C and bias by these strides
+  int64_t full_units;          // work units [0, full_units) are whole tiles, the rest 128-row halves of the
+  int64_t num_units;           // remaining tiles (MT = 2 only: balances the last, partly filled wave)
   int* status;
 };
+
+// Work unit -> (tile, first 128-row block of the tile, number of 128-row blocks).
+template <int MT>
+__device__ __forceinline__ void unit_decode(const GemmArgs& g, int64_t u, int64_t& tile, int& h0, int& nh) {
+  if (MT == 1 || u < g.full_units) {
+    tile = u;
+    h0 = 0;
+    nh = MT;
+  } else {
+    const int64_t r = u - g.full_units;
+    tile = g.full_units + (r >> 1);
+    h0 = (int)(r & 1);
+    nh = 1;
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -88,8 +105,8 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
 
 template <typename T, int MT>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    GemmArgs g) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a_half,
+                    const __grid_constant__ CUtensorMap tmap_b, GemmArgs g) {
   using namespace sm100;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -115,7 +132,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int64_t tiles_m = (g.M + TILE_M - 1) / TILE_M;
   const int64_t tiles_n = (g.N + BN - 1) / BN;
   const int64_t tiles_per_batch = tiles_m * tiles_n;
-  const int64_t num_tiles = tiles_per_batch * g.batch;
+  const int64_t num_units = g.num_units;
   const int num_kb = (int)((g.K + BK - 1) / BK);
 
   if (threadIdx.x == 0) {
@@ -130,6 +147,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_a);
+    if (MT == 2) prefetch_tmap(&tmap_a_half);
     prefetch_tmap(&tmap_b);
   }
   if (warp == 1) {
@@ -147,11 +165,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int64_t tm, tn;
+      for (int64_t u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        int64_t tile, tm, tn;
+        int h0, nh;
+        unit_decode<MT>(g, u, tile, h0, nh);
         const int bi = (int)(tile / tiles_per_batch);
         tile_coords(tile - bi * tiles_per_batch, tiles_m, tiles_n, g.group_m, tm, tn);
-        const int m0 = (int)(tm * TILE_M), n0 = (int)(tn * BN);
+        const int m0 = (int)(tm * TILE_M) + h0 * BM, n0 = (int)(tn * BN);
+        const bool whole = nh == MT;
+        const uint32_t tx_bytes = (uint32_t)(whole ? STAGE_BYTES : BM * BK * 2 + B_STAGE_BYTES);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, g.status, kStatusGemmTimeout)) {
             ok = false;
@@ -159,10 +181,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          mbar_expect_tx(&full_bar[stage], tx_bytes);
           const int k0 = kb * BK;
           if (!g.a_mn_major) {
-            tma_load_3d(sa, &tmap_a, &full_bar[stage], k0, m0, bi);
+            tma_load_3d(sa, whole ? &tmap_a : &tmap_a_half, &full_bar[stage], k0, m0, bi);
           } else {
 #pragma unroll
             for (int b = 0; b < TILE_M / 64; ++b)
@@ -194,7 +216,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       int64_t local = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int64_t u = blockIdx.x; u < num_units && ok; u += gridDim.x, ++local) {
+        const int nh = (MT == 1 || u < g.full_units) ? MT : 1;
         // MT = 1: two accumulators, used alternately.  MT = 2: both halves of TMEM hold this tile.
         const int buf = MT == 1 ? (int)(local & 1) : 0;
         const uint32_t acc_phase = MT == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
@@ -214,6 +237,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint64_t bdesc = umma_desc_sw128(sb + k * b_kstep, b_lbo, 1024);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
+              if (mt >= nh) break;
               // rows mt*128.. of the A stage: 128 rows x 128 B further on (K-major A only for MT = 2)
               const uint64_t adesc = umma_desc_sw128(sa + mt * (BM * BK * 2) + k * a_kstep, a_lbo, 1024);
               mma_f16_ss(d_tmem + (uint32_t)(mt * BN), adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
@@ -233,10 +257,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int quarter = warp & 3;          // TMEM lane quarter this warp may read
     const int chalf = (warp - 2) >> 2;     // two warps share a quarter: columns [0,128) and [128,256) of the tile
     int64_t local = 0;
-    for (int64_t tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    for (int64_t u = blockIdx.x; u < num_units; u += gridDim.x, ++local) {
       const int buf = MT == 1 ? (int)(local & 1) : 0;
       const uint32_t acc_phase = MT == 1 ? (uint32_t)((local >> 1) & 1) : (uint32_t)(local & 1);
-      int64_t tm, tn;
+      int64_t tile, tm, tn;
+      int h0, nh;
+      unit_decode<MT>(g, u, tile, h0, nh);
       const int64_t bi = tile / tiles_per_batch;
       tile_coords(tile - bi * tiles_per_batch, tiles_m, tiles_n, g.group_m, tm, tn);
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, g.status, kStatusGemmTimeout)) break;
@@ -244,8 +270,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int64_t col0 = tn * BN;
       const T* bias = reinterpret_cast<const T*>(g.bias) + bi * g.bias_bs;
 #pragma unroll 1
-      for (int mt = 0; mt < MT; ++mt) {
-      const int64_t row = tm * TILE_M + mt * BM + quarter * 32 + lane;
+      for (int mt = 0; mt < nh; ++mt) {
+      const int64_t row = tm * TILE_M + (h0 + mt) * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf + mt) * BN);
       T* crow = reinterpret_cast<T*>(g.c) + bi * g.c_bs + row * g.c_s0;
 #pragma unroll 1
@@ -320,11 +346,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
 // Cost of a 256x256 tile relative to two 128x256 tiles (tile-shape choice below).
 constexpr double kBigTileCost = 0.85;
+// Cost of a 128-row half of a 256x256 tile in tile times.
+constexpr double kHalfTileCost = 0.56;
 // 0: choose; 1 / 2: force the tile shape (set from the environment variable FLAGGEMS_B200_GEMM_MT,
 // for measurements).
 static const int g_force_mt = []() {
   const char* e = getenv("FLAGGEMS_B200_GEMM_MT");
   return e ? atoi(e) : 0;
+}();
+
+// FLAGGEMS_B200_GEMM_SPLIT_TAIL=0 keeps the last wave of 256x256 tiles whole (for measurements).
+static const bool g_split_tail = []() {
+  const char* e = getenv("FLAGGEMS_B200_GEMM_SPLIT_TAIL");
+  return !(e && atoi(e) == 0);
 }();
 
 static bool tcgen05_eligible(const fg_gemm_params* p) {
@@ -349,7 +383,8 @@ static bool tcgen05_eligible(const fg_gemm_params* p) {
 }
 
 template <typename T, int MT>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& g, int grid, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& ta_half, const CUtensorMap& tb, const GemmArgs& g,
+                       int grid, cudaStream_t st) {
   static thread_local int attr_dev = -1;
   int dev = 0;
   cudaGetDevice(&dev);
@@ -358,7 +393,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
                                     SMEM_BYTES));
     attr_dev = dev;
   }
-  gemm_tcgen05_kernel<T, MT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, tb, g);
+  gemm_tcgen05_kernel<T, MT><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ta, ta_half, tb, g);
   FG_CHECK_LAUNCH("gemm_tcgen05_kernel");
   return FG_OK;
 }
@@ -380,12 +415,17 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
   const int64_t tn = (p->N + BN - 1) / BN;
   const int64_t tiles1 = ((p->M + BM - 1) / BM) * tn * bt.batch;
   const int64_t tiles2 = ((p->M + 2 * BM - 1) / (2 * BM)) * tn * bt.batch;
-  const int64_t waves1 = (tiles1 + sms - 1) / sms, waves2 = (tiles2 + sms - 1) / sms;
-  int mt = (!a_mn && p->M > BM && (double)waves2 * 2.0 * kBigTileCost < (double)waves1) ? 2 : 1;
+  const int64_t waves1 = (tiles1 + sms - 1) / sms;
+  // A last wave of 256x256 tiles that fills at most half of the SMs is cut into 128-row halves,
+  // one per CTA: it then takes about 0.56 of a tile time (one MMA per K step, B no longer shared).
+  const int64_t rest2 = tiles2 % sms;
+  const bool split_tail = g_split_tail && tiles2 > sms && rest2 > 0 && 2 * rest2 <= sms;
+  const double waves2 = (double)(tiles2 / sms) + (rest2 == 0 ? 0.0 : split_tail ? kHalfTileCost : 1.0);
+  int mt = (!a_mn && p->M > BM && waves2 * 2.0 * kBigTileCost < (double)waves1) ? 2 : 1;
   if (g_force_mt == 1 || (g_force_mt == 2 && !a_mn)) mt = g_force_mt;
   const int tile_m = mt * BM;
 
-  CUtensorMap ta, tb;
+  CUtensorMap ta, ta_half, tb;
   {
     // third dimension: the batch (extent 1 and a dummy stride for a plain GEMM)
     uint64_t dims[3], strides[2];
@@ -402,6 +442,12 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
     strides[1] = bt.batch > 1 ? (uint64_t)bt.a_bs * 2 : strides[0] * dims[1];
     int rc = encode_tmap_16bit(&ta, p->a, 3, dims, strides, box);
     if (rc != FG_OK) return rc;
+    ta_half = ta;
+    if (mt == 2) {  // the same matrix in boxes of 128 rows, for the halved tiles of the last wave
+      box[1] = BM;
+      rc = encode_tmap_16bit(&ta_half, p->a, 3, dims, strides, box);
+      if (rc != FG_OK) return rc;
+    }
     if (!b_mn) {
       dims[0] = (uint64_t)p->K; dims[1] = (uint64_t)p->N; strides[0] = (uint64_t)p->b_stride1 * 2;
       box[0] = 64; box[1] = BN;
@@ -442,9 +488,12 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
   const int64_t tiles = mt == 2 ? tiles2 : tiles1;
   int grid = sms;  // persistent: one CTA per SM it may use
   if (tiles < grid) grid = (int)tiles;
+  g.full_units = (mt == 2 && split_tail) ? tiles - rest2 : tiles;
+  g.num_units = g.full_units + 2 * (tiles - g.full_units);
   if (p->dtype == FG_BF16)
-    return mt == 2 ? launch_gemm<__nv_bfloat16, 2>(ta, tb, g, grid, st) : launch_gemm<__nv_bfloat16, 1>(ta, tb, g, grid, st);
-  return mt == 2 ? launch_gemm<__half, 2>(ta, tb, g, grid, st) : launch_gemm<__half, 1>(ta, tb, g, grid, st);
+    return mt == 2 ? launch_gemm<__nv_bfloat16, 2>(ta, ta_half, tb, g, grid, st)
+                   : launch_gemm<__nv_bfloat16, 1>(ta, ta_half, tb, g, grid, st);
+  return mt == 2 ? launch_gemm<__half, 2>(ta, ta_half, tb, g, grid, st) : launch_gemm<__half, 1>(ta, ta_half, tb, g, grid, st);
 }
 
 bool gemm_tcgen05_eligible(const fg_gemm_params* p) { return tcgen05_eligible(p); }

@@ -19,7 +19,7 @@ from . import _lib
 logger = logging.getLogger("flag_gems." + __name__.split(".")[-1])
 
 __all__ = ["mm", "mm_out", "addmm", "addmm_out", "bmm", "flash_attn_varlen_func", "flash_attention_forward", "rms_norm",
-           "get_higher_dtype"]
+           "get_scheduler_metadata", "scheduler_plan", "get_higher_dtype"]
 
 _ordered_datatypes = [torch.float16, torch.bfloat16, torch.float32]
 
@@ -457,3 +457,97 @@ def flash_attention_forward(
     unused = torch.empty(0, dtype=torch.int64, device=query.device)
     debug_mask = torch.empty(0, dtype=query.dtype, device=query.device)
     return res.view(B, Sq, H, D), lse, rng_state, unused, debug_mask
+
+
+def _scheduler_params(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v, qkv_dtype,
+                      page_size, max_seqlen_k_new, is_causal, window_size_left, window_size_right, has_softcap,
+                      num_splits, pack_gqa, sm_margin, arch, num_sm, varlen_q=False, has_leftpad=False):
+    if qkv_dtype not in (torch.half, torch.bfloat16):
+        raise AssertionError("FlashAttention only supports fp16 and bf16 data type")
+    if num_heads % num_heads_k != 0:
+        raise AssertionError("Number of heads in key/value must divide number of heads in query")
+    p = _lib.SchedulerParams()
+    p.batch_size, p.max_seqlen_q, p.max_seqlen_k = batch_size, max_seqlen_q, max_seqlen_k
+    p.num_heads, p.num_heads_k, p.headdim, p.headdim_v = num_heads, num_heads_k, headdim, headdim_v
+    p.elem_size = qkv_dtype.itemsize
+    p.page_size = 0 if page_size is None else int(page_size)
+    p.max_seqlen_k_new, p.is_causal = max_seqlen_k_new, int(bool(is_causal))
+    p.window_size_left, p.window_size_right = window_size_left, window_size_right
+    p.has_softcap, p.num_splits = int(bool(has_softcap)), num_splits
+    p.pack_gqa = -1 if pack_gqa is None else int(bool(pack_gqa))
+    p.sm_margin, p.arch, p.num_sm = sm_margin, arch, num_sm
+    p.varlen_q, p.has_leftpad = int(varlen_q), int(has_leftpad)
+    return p
+
+
+def scheduler_plan(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v,
+                   qkv_dtype=torch.bfloat16, *, page_size=None, max_seqlen_k_new=0, is_causal=False,
+                   window_size_left=-1, window_size_right=-1, has_softcap=False, num_splits=0, pack_gqa=None,
+                   sm_margin=0, varlen_q=False, has_leftpad=False, arch=100, num_sm=148) -> dict:
+    """The host half of ``get_scheduler_metadata`` (no device work): static split count,
+    pack-GQA choice and the tile the block counts refer to, as a dict."""
+    p = _scheduler_params(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v,
+                          qkv_dtype, page_size, max_seqlen_k_new, is_causal, window_size_left, window_size_right,
+                          has_softcap, num_splits, pack_gqa, sm_margin, arch, num_sm, varlen_q, has_leftpad)
+    plan = _lib.SchedulerPlan()
+    _lib.check(_lib.load().fg_scheduler_plan(C.byref(p), C.byref(plan)))
+    return {name: getattr(plan, name) for name, _ in plan._fields_}
+
+
+def get_scheduler_metadata(
+    batch_size: int,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    num_heads: int,
+    num_heads_k: int,
+    headdim: int,
+    headdim_v: int,
+    qkv_dtype: torch.dtype,
+    seqused_k: torch.Tensor,
+    cu_seqlens_q=None,
+    cu_seqlens_k=None,
+    cu_seqlens_k_new=None,
+    seqused_q=None,
+    leftpad_k=None,
+    page_size=None,
+    max_seqlen_k_new: int = 0,
+    is_causal: bool = False,
+    window_size_left: int = -1,
+    window_size_right: int = -1,
+    has_softcap: bool = False,
+    num_splits: int = 0,
+    pack_gqa=None,
+    sm_margin: int = 0,
+) -> torch.Tensor:
+    """Split-KV scheduling vector ``[semaphore, splits per sequence]`` (int32) of a
+    FlashAttention-3 style decode; signature and result of
+    ``src/flag_gems/ops/get_scheduler_metadata.py:567-894``.  One kernel launch and no
+    device-to-host read (the reference reads the block total back between two kernels)."""
+    logger.debug("GEMS GET_SCHEDULER_METADATA")
+    dev = _lib.require_cuda(seqused_k, cu_seqlens_q, cu_seqlens_k_new, seqused_q, leftpad_k)
+    cap = torch.cuda.get_device_capability(dev)
+    p = _scheduler_params(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v,
+                          qkv_dtype, page_size, max_seqlen_k_new, is_causal, window_size_left, window_size_right,
+                          has_softcap, num_splits, pack_gqa, sm_margin, cap[0] * 10 + cap[1],
+                          torch.cuda.get_device_properties(dev).multi_processor_count)
+    keep = []
+
+    def ptr(t, n, name):
+        if t is None:
+            return None
+        if t.numel() < n:
+            raise RuntimeError(f"get_scheduler_metadata: {name} has {t.numel()} entries, {n} needed")
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            t = t.to(torch.int32).contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    p.seqused_k = ptr(seqused_k, batch_size, "seqused_k")
+    p.cu_seqlens_q = ptr(cu_seqlens_q, batch_size + 1, "cu_seqlens_q")
+    p.cu_seqlens_k_new = ptr(cu_seqlens_k_new, batch_size + 1, "cu_seqlens_k_new")
+    p.seqused_q = ptr(seqused_q, batch_size, "seqused_q")
+    p.leftpad_k = ptr(leftpad_k, batch_size, "leftpad_k")
+    out = torch.empty(1 + (batch_size if batch_size <= 992 else 0), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().fg_get_scheduler_metadata(C.byref(p), out.data_ptr(), _lib.stream_ptr(dev)))
+    return out

@@ -1,6 +1,6 @@
 """vLLM integration (mirror of ``src/flag_gems/patches/patch_vllm_all.py`` for the
 inference path): the replacement methods keep the reference's signatures; the MLA /
-MoE / top-k / scheduler-metadata patches of the reference are outside this path.
+MoE / top-k patches of the reference are outside this path.
 
 ``apply_gems_patches_to_vllm`` looks the vLLM classes up defensively because their
 module paths move between vLLM releases; a class that cannot be found is skipped and
@@ -25,6 +25,7 @@ __all__ = [
     "custom_gems_write_to_paged_cache",
     "custom_gems_flash_attention_impl_forward",
     "custom_silu_and_mul",
+    "custom_get_scheduler_metadata",
 ]
 
 _libs: dict = {}
@@ -94,6 +95,20 @@ def custom_gems_write_to_paged_cache(key, value, key_cache, value_cache, slot_ma
     """``PagedAttention.write_to_paged_cache`` (vLLM v0 cache layout), patch_vllm_all.py:71-92."""
     fused.reshape_and_cache(key, value, key_cache, value_cache, slot_mapping.flatten(), kv_cache_dtype, k_scale,
                             v_scale)
+
+
+def custom_get_scheduler_metadata(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v,
+                                  qkv_dtype, seqused_k, cu_seqlens_q=None, cu_seqlens_k=None, cu_seqlens_k_new=None,
+                                  seqused_q=None, leftpad_k=None, page_size=None, max_seqlen_k_new=0, is_causal=False,
+                                  window_size_left=-1, window_size_right=-1, has_softcap=False, num_splits=0,
+                                  pack_gqa=None, sm_margin=0):
+    """Replacement of ``torch.ops._vllm_fa3_C.get_scheduler_metadata`` (patch_vllm_all.py:279-328)."""
+    return ops.get_scheduler_metadata(
+        batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v, qkv_dtype, seqused_k,
+        cu_seqlens_q=cu_seqlens_q, cu_seqlens_k=cu_seqlens_k, cu_seqlens_k_new=cu_seqlens_k_new, seqused_q=seqused_q,
+        leftpad_k=leftpad_k, page_size=page_size, max_seqlen_k_new=max_seqlen_k_new, is_causal=is_causal,
+        window_size_left=window_size_left, window_size_right=window_size_right, has_softcap=has_softcap,
+        num_splits=num_splits, pack_gqa=pack_gqa, sm_margin=sm_margin)
 
 
 def custom_silu_and_mul(out: torch.Tensor, input: torch.Tensor):
@@ -200,10 +215,12 @@ def apply_gems_patches_to_vllm(verbose=True):
             continue
         patch_module_method(cls, method, fn, verbose)
         patched.append(f"{cls.__name__}.{method}")
-    try:
-        patch_vllm_lib("_C", "silu_and_mul", custom_silu_and_mul, "CUDA", verbose)
-        patched.append("_C.silu_and_mul")
-    except Exception as e:  # the op namespace exists only once vLLM's extension is loaded
-        if verbose:
-            print(f"FLAGGEMS: torch.ops._C.silu_and_mul not patched ({e})")
+    for lib_name, fn_name, fn in (("_C", "silu_and_mul", custom_silu_and_mul),
+                                  ("_vllm_fa3_C", "get_scheduler_metadata", custom_get_scheduler_metadata)):
+        try:
+            patch_vllm_lib(lib_name, fn_name, fn, "CUDA", verbose)
+            patched.append(f"{lib_name}.{fn_name}")
+        except Exception as e:  # the op namespace exists only once vLLM's extension is loaded
+            if verbose:
+                print(f"FLAGGEMS: torch.ops.{lib_name}.{fn_name} not patched ({e})")
     return patched

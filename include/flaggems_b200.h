@@ -290,6 +290,48 @@ FG_API int fg_flash_attn_path(const fg_attn_params* p);
 FG_API int fg_flash_attn_decode_static(const fg_attn_params* p, void* stream);
 FG_API int64_t fg_flash_attn_decode_static_capacity(void);
 
+/* ------------------------------------------------------------------------
+ * get_scheduler_metadata: split-KV scheduling vector of a FlashAttention-3 style
+ * decode.  Replaces get_scheduler_metadata
+ * (src/flag_gems/ops/get_scheduler_metadata.py:567-894; bound by vLLM as
+ * _vllm_fa3_C.get_scheduler_metadata, src/flag_gems/patches/patch_vllm_all.py:279-368)
+ * for compute capability >= 9.0; older parts return FG_ERR_UNSUPPORTED.
+ *
+ * fg_scheduler_plan is host arithmetic only (no CUDA call): the normalised mask kind,
+ * the pack-GQA choice, the static split count and the tile (block_m x block_n) the
+ * per-sequence block counts are taken in.  metadata_len = 1 + batch_size for batches
+ * of at most 992 sequences, else 1.
+ * fg_get_scheduler_metadata enqueues ONE kernel on `stream` that writes
+ *   metadata[0] = 0 (work-queue semaphore), metadata[1 + b] = KV splits of sequence b
+ * into `metadata` (device, metadata_len int32).  No host synchronisation (the reference
+ * reads the block total back between its two kernels).  Integer result, identical to
+ * the reference's.
+ *   page_size 0 = no page table; pack_gqa -1 = decide by heuristic; num_splits <= 0 =
+ *   decide by heuristic; arch = 10 * major + minor; num_sm = SMs of the device.
+ *   cu_seqlens_k is accepted for signature parity and not read (nor does the reference).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v;
+  int32_t elem_size;        /* bytes per q/k/v element: 2 */
+  int32_t page_size, max_seqlen_k_new, is_causal, window_size_left, window_size_right;
+  int32_t has_softcap, num_splits, pack_gqa, sm_margin, arch, num_sm;
+  int32_t varlen_q, has_leftpad; /* for fg_scheduler_plan without device pointers */
+  const int32_t* seqused_k;        /* [batch] device, required by fg_get_scheduler_metadata */
+  const int32_t* cu_seqlens_q;     /* [batch + 1] or NULL */
+  const int32_t* cu_seqlens_k;     /* unused */
+  const int32_t* cu_seqlens_k_new; /* [batch + 1] or NULL */
+  const int32_t* seqused_q;        /* [batch] or NULL */
+  const int32_t* leftpad_k;        /* [batch] or NULL */
+} FgSchedulerParams;
+
+typedef struct {
+  int32_t num_splits, pack_gqa, block_m, block_n, use_dynamic_split, is_causal, is_local;
+  int32_t q_per_kv, heads, metadata_len;
+} FgSchedulerPlan;
+
+FG_API int fg_scheduler_plan(const FgSchedulerParams* p, FgSchedulerPlan* plan);
+FG_API int fg_get_scheduler_metadata(const FgSchedulerParams* p, int32_t* metadata, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

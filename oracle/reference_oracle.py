@@ -274,3 +274,178 @@ def bmm(a: torch.Tensor, b: torch.Tensor, upcast: torch.dtype = torch.float64) -
 def addmm(bias, mat1, mat2, alpha=1.0, beta=1.0, upcast: torch.dtype = torch.float64) -> torch.Tensor:
     """``torch.addmm`` on upcast inputs (tests/test_blas_ops.py:38-44)."""
     return torch.addmm(bias.to(upcast), mat1.to(upcast), mat2.to(upcast), alpha=alpha, beta=beta)
+
+
+# ---------------------------------------------------------------------------------------
+# get_scheduler_metadata (split-KV scheduling of the FlashAttention-3 style decode),
+# ops/get_scheduler_metadata.py.  Restated for compute capability >= 9.0 only (the
+# sm8x tile table, :12-88, is not reachable on a B200); integer work, bit-exact.
+# Pinned by tests/golden/golden_scheduler_metadata.pt, produced by running the reference
+# function itself under Triton's interpreter with the device queries answered
+# (10, 0) / 148 SMs.
+# ---------------------------------------------------------------------------------------
+
+def _round_head_dim(d: int, last: int) -> int:
+    """ops/get_scheduler_metadata.py:191-216 (``last`` = 256 for qk, 512 for v)."""
+    for step in (64, 96, 128, 192, 256):
+        if d <= step:
+            return step
+    return last
+
+
+def _tile_mn_sm90(d: int, dv: int, causal: bool, local: bool, paged_non_tma: bool, one_wg: bool):
+    """(kBlockM, kBlockN) for 16-bit inputs, ops/get_scheduler_metadata.py:91-127."""
+    if d <= 64:
+        if dv == 512:
+            return 64, 64
+        if dv == 256:
+            return 128, 112
+        return 192, (128 if (causal or local) else 192)
+    if d <= 96:
+        return 192, (128 if (local or paged_non_tma) else 144)
+    if d <= 128:
+        return (64 if one_wg else 128), (128 if (causal or local or paged_non_tma) else 176)
+    if d <= 192:
+        return 128, (96 if (paged_non_tma or local) else (128 if dv <= 128 else 112))
+    return 128, (64 if local else 80)
+
+
+def _one_mma_warpgroup(headdim: int, seqlen_q: int, pack_gqa: bool, hq: int, hk: int) -> bool:
+    """ops/get_scheduler_metadata.py:261-275."""
+    return headdim == 128 and seqlen_q * ((hq // hk) if pack_gqa else 1) <= 64
+
+
+def _split_heuristic(total_mblocks: int, num_sm: int, n_blocks: int, m_blocks: int, bytes_one_kv_head: int,
+                     causal_or_local: bool, max_splits: int) -> int:
+    """ops/get_scheduler_metadata.py:393-426 (double-precision efficiencies, as Python floats)."""
+    import math
+    if total_mblocks >= 0.8 * num_sm:
+        l2 = 50 * 1024 * 1024
+        if bytes_one_kv_head > l2 and m_blocks >= num_sm * 2 and not causal_or_local:
+            return min(-(-bytes_one_kv_head // l2), max_splits)
+        return 1
+    if n_blocks <= 4:
+        return 1
+    max_splits = min(max_splits, num_sm, n_blocks)
+    eff = []
+    for s in range(1, max_splits + 1):
+        waves = float(total_mblocks * s) / num_sm
+        eff.append(waves / math.ceil(waves))
+    best = max(eff) if eff else 0.0
+    for s, e in enumerate(eff, start=1):
+        if e >= 0.85 * best:
+            return s
+    return 1
+
+
+def scheduler_plan(batch_size: int, max_seqlen_q: int, max_seqlen_k: int, num_heads: int, num_heads_k: int,
+                   headdim: int, headdim_v: int, *, page_size: Optional[int] = None, has_leftpad: bool = False,
+                   varlen_q: bool = False, max_seqlen_k_new: int = 0, is_causal: bool = False,
+                   window_size_left: int = -1, window_size_right: int = -1, has_softcap: bool = False,
+                   num_splits: int = 0, pack_gqa: Optional[bool] = None, num_sm: int = 148) -> dict:
+    """The host half of get_scheduler_metadata, ops/get_scheduler_metadata.py:592-769:
+    mask normalisation, pack-GQA choice, static split count and the tile the block counts
+    are taken in."""
+    elem = 2
+    wl = window_size_left if window_size_left >= 0 else -1
+    wr = window_size_right
+    if wl >= max_seqlen_k - 1:
+        wl = -1
+    if wr >= max_seqlen_q - 1:
+        wr = -1
+    causal = bool(is_causal)
+    if max_seqlen_q == 1 and wl == -1 and wr == -1 and ((headdim <= 64 or headdim > 128) or page_size is None):
+        causal = False
+    if causal:
+        wr = 0
+    causal = wl < 0 and wr == 0
+    local = (wl >= 0 or wr >= 0) and not causal
+    paged = page_size is not None
+    d_r, dv_r = _round_head_dim(headdim, 256), _round_head_dim(headdim_v, 512)
+    group = num_heads // num_heads_k
+
+    # paged K/V through TMA: whole pages per key tile and more than one query tile (:219-258)
+    paged_tma = False
+    if paged and not has_leftpad and max_seqlen_k_new == 0:
+        bm, bn = _tile_mn_sm90(d_r, dv_r, causal, local, False, False)
+        paged_tma = page_size % bn == 0 and max_seqlen_q * group > bm
+
+    if pack_gqa is None:  # :535-564, :278-293
+        if (paged and not paged_tma) or num_splits > 1:
+            pack_gqa = True
+        elif num_heads == num_heads_k:
+            pack_gqa = False
+        elif varlen_q:
+            pack_gqa = True
+        else:
+            bm, _ = _tile_mn_sm90(d_r, dv_r, causal, local, paged and not paged_tma, False)
+            up = lambda a: -(-a // bm) * bm
+            pack_gqa = float(max_seqlen_q) / up(max_seqlen_q) < 0.9 * (float(max_seqlen_q * group) / up(max_seqlen_q * group))
+
+    dynamic = batch_size <= 992
+    if num_splits <= 0:  # :296-390; inside, paged K/V always counts as the non-TMA form
+        bm, bn = _tile_mn_sm90(d_r, dv_r, causal, local, paged, _one_mma_warpgroup(headdim, max_seqlen_q, pack_gqa,
+                                                                                     num_heads, num_heads_k))
+        k_loaded = max(0, min(max_seqlen_k, wl + wr + 1 + bm)) if local else max_seqlen_k
+        n_blocks, m_blocks = -(-k_loaded // bn), -(-(max_seqlen_q * group) // bm)
+        splits = _split_heuristic((1 if dynamic else batch_size) * num_heads_k * m_blocks, num_sm, n_blocks, m_blocks,
+                                  max_seqlen_k * (headdim + headdim_v) * elem, causal or local, 128)
+    else:
+        splits = num_splits
+    splits = min(splits, 256, num_sm)
+    if splits > 1:
+        pack_gqa = True
+    bm, bn = _tile_mn_sm90(d_r, dv_r, causal, local, paged and not paged_tma,
+                           _one_mma_warpgroup(headdim, max_seqlen_q, pack_gqa, num_heads, num_heads_k))
+    return dict(num_splits=splits, pack_gqa=bool(pack_gqa), block_m=bm, block_n=bn, dynamic=dynamic, causal=causal,
+                local=local, q_per_kv=(-(-num_heads // num_heads_k)) if pack_gqa else 1,
+                heads=num_heads_k if pack_gqa else num_heads)
+
+
+def get_scheduler_metadata(batch_size: int, max_seqlen_q: int, max_seqlen_k: int, num_heads: int, num_heads_k: int,
+                           headdim: int, headdim_v: int, seqused_k: torch.Tensor,
+                           cu_seqlens_q: Optional[torch.Tensor] = None, cu_seqlens_k_new: Optional[torch.Tensor] = None,
+                           seqused_q: Optional[torch.Tensor] = None, leftpad_k: Optional[torch.Tensor] = None,
+                           page_size: Optional[int] = None, max_seqlen_k_new: int = 0, is_causal: bool = False,
+                           window_size_left: int = -1, window_size_right: int = -1, has_softcap: bool = False,
+                           num_splits: int = 0, pack_gqa: Optional[bool] = None, sm_margin: int = 0,
+                           sm_count: int = 148) -> torch.Tensor:
+    """int32 ``[semaphore = 0, splits of sequence 0, 1, ...]`` (the per-sequence part only for
+    batches of at most 992), ops/get_scheduler_metadata.py:567-894; the two device passes
+    are :430-532 (per-sequence tile counts and their sum; then KV tiles per SM in fp32)."""
+    import numpy as np
+    num_sm = sm_count - sm_margin
+    plan = scheduler_plan(batch_size, max_seqlen_q, max_seqlen_k, num_heads, num_heads_k, headdim, headdim_v,
+                          page_size=page_size, has_leftpad=leftpad_k is not None,
+                          varlen_q=cu_seqlens_q is not None or seqused_q is not None,
+                          max_seqlen_k_new=max_seqlen_k_new, is_causal=is_causal, window_size_left=window_size_left,
+                          window_size_right=window_size_right, has_softcap=has_softcap, num_splits=num_splits,
+                          pack_gqa=pack_gqa, num_sm=num_sm)
+    if not plan["dynamic"]:
+        return torch.zeros(1, dtype=torch.int32)
+    as_np = lambda t: t.detach().cpu().numpy().astype(np.int64)
+    if seqused_q is not None:
+        q_len = as_np(seqused_q)[:batch_size]
+    elif cu_seqlens_q is not None:
+        q_len = np.diff(as_np(cu_seqlens_q)[:batch_size + 1])
+    else:
+        q_len = np.full(batch_size, max_seqlen_q, dtype=np.int64)
+    m_blocks = (q_len * plan["q_per_kv"] + plan["block_m"] - 1) // plan["block_m"]
+    k_len = as_np(seqused_k)[:batch_size]
+    if max_seqlen_k_new > 0:
+        k_len = k_len + (np.diff(as_np(cu_seqlens_k_new)[:batch_size + 1]) if cu_seqlens_k_new is not None
+                         else max_seqlen_k_new)
+    if leftpad_k is not None:
+        k_len = k_len - as_np(leftpad_k)[:batch_size]
+    n_blocks = (k_len + plan["block_n"] - 1) // plan["block_n"]
+    total = int((m_blocks * n_blocks).sum())
+    if max_seqlen_k_new > 0 and cu_seqlens_k_new is None and seqused_q is None and cu_seqlens_q is None:
+        # The first pass works in programs of 128 sequences (:467-506) and its sum is not masked: a lane past
+        # the batch reads 0 keys but still gets the constant query length and the constant appended length,
+        # so every padding lane adds one sequence of max_seqlen_q queries and max_seqlen_k_new keys.
+        pad = -batch_size % 128
+        total += pad * int(-(-(max_seqlen_q * plan["q_per_kv"]) // plan["block_m"])) * int(-(-max_seqlen_k_new // plan["block_n"]))
+    f = np.float32
+    per_sm = max(1, int(np.ceil(f(f(f(total) * f(1.1)) * f(plan["heads"])) / f(num_sm))))
+    splits = np.maximum(1, np.minimum((n_blocks + per_sm - 1) // per_sm, plan["num_splits"]))
+    return torch.from_numpy(np.concatenate([[0], splits]).astype(np.int32))

@@ -385,3 +385,88 @@ def test_sdpa_through_use_gems_and_gqa(fg):
     torch.testing.assert_close(o.transpose(1, 2).cpu().float(), refg, atol=ATOL, rtol=RTOL)
     with pytest.raises(NotImplementedError):
         fg.flash_attention_forward(qg, kg, vg, None, None, 256, 300, 0.1, True, False)
+
+
+# ---------------------------------------------------------------------------------------
+# get_scheduler_metadata: integer work, bit-exact against the fixture recorded from the
+# reference function itself, against the oracle on fresh random inputs, and for the
+# reference test's own grid (tests/test_attention_ops.py:1618-1695).
+# ---------------------------------------------------------------------------------------
+
+def _sched_to(kw, device):
+    return {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in kw.items()}
+
+
+@pytest.mark.gpu
+def test_scheduler_metadata_golden(fg, golden_dir):
+    props = torch.cuda.get_device_properties(0)
+    cases = torch.load(golden_dir / "golden_scheduler_metadata.pt", weights_only=False)
+    if props.multi_processor_count != cases[0]["sm_count"]:
+        pytest.skip(f"fixture recorded for {cases[0]['sm_count']} SMs, this GPU has {props.multi_processor_count}")
+    for i, c in enumerate(cases):
+        got = fg.get_scheduler_metadata(**_sched_to(c["kwargs"], DEV))
+        assert got.dtype == torch.int32 and got.is_cuda
+        assert torch.equal(got.cpu(), c["metadata"]), (i, {k: v for k, v in c["kwargs"].items()
+                                                          if not torch.is_tensor(v)})
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch_size", [1, 8, 256, 512])
+@pytest.mark.parametrize("max_seqlen_k", [512, 2048])
+@pytest.mark.parametrize("headdim", [64, 128])
+@pytest.mark.parametrize("num_splits_static", [0, 4])
+def test_scheduler_metadata_reference_grid(fg, batch_size, max_seqlen_k, headdim, num_splits_static):
+    g = torch.Generator().manual_seed(42 + batch_size + max_seqlen_k)
+    seqused_k = torch.randint(1, max_seqlen_k, (batch_size,), dtype=torch.int32, generator=g)
+    kw = dict(batch_size=batch_size, max_seqlen_q=1, max_seqlen_k=max_seqlen_k, num_heads=32, num_heads_k=8,
+              headdim=headdim, headdim_v=headdim, cu_seqlens_q=None, cu_seqlens_k_new=None, seqused_q=None,
+              leftpad_k=None, page_size=None, max_seqlen_k_new=0, is_causal=False, window_size_left=-1,
+              window_size_right=-1, has_softcap=False, num_splits=num_splits_static, pack_gqa=True, sm_margin=0)
+    with fg.use_gems():
+        got = fg.get_scheduler_metadata(qkv_dtype=torch.float16, seqused_k=seqused_k.to(DEV), cu_seqlens_k=None, **kw)
+    want = O.get_scheduler_metadata(seqused_k=seqused_k, sm_count=torch.cuda.get_device_properties(0).multi_processor_count,
+                                    **kw)
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.gpu
+def test_scheduler_metadata_random_and_edges(fg):
+    import random
+
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    rng = random.Random(11)
+    g = torch.Generator().manual_seed(11)
+    ri = lambda lo, hi, n: torch.randint(lo, hi, (n,), dtype=torch.int32, generator=g)
+    for _ in range(150):
+        b = rng.choice([0, 1, 2, 5, 127, 128, 129, 992, 993, 1024, 1025, 5000])
+        hk = rng.choice([1, 2, 8])
+        hq = hk * rng.choice([1, 4, 7, 16])
+        d = rng.choice([64, 96, 128, 192, 256])
+        sq, sk = rng.choice([1, 1, 3, 64, 500]), rng.choice([16, 512, 8192, 70000, 300000])
+        kw = dict(batch_size=b, max_seqlen_q=sq, max_seqlen_k=sk, num_heads=hq, num_heads_k=hk, headdim=d,
+                  headdim_v=rng.choice([d, 128, 512]), seqused_k=ri(1, sk + 1, b), cu_seqlens_q=None,
+                  cu_seqlens_k_new=None, seqused_q=None, leftpad_k=None, page_size=rng.choice([None, 16, 128]),
+                  max_seqlen_k_new=rng.choice([0, 0, 4, 300]), is_causal=rng.random() < 0.5,
+                  window_size_left=rng.choice([-1, -1, 100]), window_size_right=rng.choice([-1, 0, 50]),
+                  has_softcap=rng.random() < 0.2, num_splits=rng.choice([0, 0, 1, 3, 300]),
+                  pack_gqa=rng.choice([None, True, False]), sm_margin=rng.choice([0, 16]))
+        r = rng.random()
+        if r < 0.25:
+            ql = ri(1, sq + 1, b)
+            kw["cu_seqlens_q"] = torch.cat([torch.zeros(1, dtype=torch.int32), ql.cumsum(0).to(torch.int32)])
+        elif r < 0.5:
+            kw["seqused_q"] = ri(1, sq + 1, b)
+        if rng.random() < 0.3:
+            kw["leftpad_k"] = torch.minimum(ri(0, 40, b), kw["seqused_k"] - 1)
+        if kw["max_seqlen_k_new"] and rng.random() < 0.5:
+            kn = ri(1, kw["max_seqlen_k_new"] + 1, b)
+            kw["cu_seqlens_k_new"] = torch.cat([torch.zeros(1, dtype=torch.int32), kn.cumsum(0).to(torch.int32)])
+        want = O.get_scheduler_metadata(sm_count=sms, **kw)
+        got = fg.get_scheduler_metadata(qkv_dtype=torch.bfloat16, cu_seqlens_k=None, **_sched_to(kw, DEV))
+        assert torch.equal(got.cpu(), want), {k: v for k, v in kw.items() if not torch.is_tensor(v)}
+    # int64 length vectors are converted; too short a vector is refused
+    sk = torch.tensor([700, 9000, 33], dtype=torch.int64, device=DEV)
+    a = fg.get_scheduler_metadata(3, 1, 9000, 32, 8, 128, 128, torch.bfloat16, sk, page_size=16)
+    assert torch.equal(a.cpu(), O.get_scheduler_metadata(3, 1, 9000, 32, 8, 128, 128, sk.cpu(), page_size=16, sm_count=sms))
+    with pytest.raises(RuntimeError, match="entries"):
+        fg.get_scheduler_metadata(4, 1, 9000, 32, 8, 128, 128, torch.bfloat16, sk)

@@ -63,7 +63,10 @@ def test_addmm(fg, M, N, K, scalar, dtype, b_column_major):
 
 
 TC_SHAPES = [(128, 256, 64), (256, 512, 4096), (1000, 776, 520), (4096, 4096, 4096), (129, 264, 72), (64, 64, 32),
-             (2048, 6144, 4096), (300, 16, 4096), (8, 3000, 128)]
+             (2048, 6144, 4096), (300, 16, 4096), (8, 3000, 128),
+             # 256x256 tiles whose last wave is cut into 128-row halves (162, 896 and 512 tiles on 148 SMs),
+             # the first with a ragged last row tile
+             (2100, 4608, 512), (2048, 28672, 256), (8192, 4096, 512)]
 
 
 @pytest.mark.parametrize("M,N,K", TC_SHAPES)

@@ -86,3 +86,23 @@ def test_flash_attn_varlen_prefill_and_decode_vs_triton(fg, ref):
     torch.testing.assert_close(fg.flash_attn_varlen_func(d.q, d.key_cache, d.value_cache, **kw).float(),
                                ref.flash_attn_varlen_func(d.q, d.key_cache, d.value_cache, **kw).float(),
                                atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.gpu
+def test_get_scheduler_metadata_vs_triton(fg, ref):
+    g = torch.Generator().manual_seed(42)
+    for b, sk, d, ns, page, knew in [(1, 512, 64, 0, None, 0), (8, 2048, 128, 0, None, 0), (256, 2048, 128, 4, None, 0),
+                                     (512, 512, 64, 0, None, 0), (256, 8192, 128, 0, 16, 0), (64, 32768, 128, 0, 16, 0),
+                                     (993, 8192, 128, 0, 16, 0), (5, 6000, 64, 0, None, 5), (130, 6000, 128, 0, 16, 0)]:
+        seqused_k = torch.randint(1, sk, (b,), dtype=torch.int32, generator=g).to(DEV)
+        kw = dict(batch_size=b, max_seqlen_q=1, max_seqlen_k=sk, num_heads=32, num_heads_k=8, headdim=d, headdim_v=d,
+                  qkv_dtype=torch.float16, seqused_k=seqused_k, cu_seqlens_q=None, cu_seqlens_k=None,
+                  cu_seqlens_k_new=None, seqused_q=None, leftpad_k=None, page_size=page, max_seqlen_k_new=knew,
+                  is_causal=False, window_size_left=-1, window_size_right=-1, has_softcap=False, num_splits=ns,
+                  pack_gqa=None if page else True, sm_margin=0)
+        try:
+            want = ref.get_scheduler_metadata(**kw)
+        except Exception as e:  # the reference's kernels against this image's Triton
+            pytest.skip(f"reference get_scheduler_metadata does not run here: {type(e).__name__}: {e}")
+        got = fg.get_scheduler_metadata(**kw)
+        assert torch.equal(got, want.to(torch.int32)), (b, sk, d, ns, page, knew)

@@ -164,3 +164,43 @@ def test_workload_generators_are_seeded_and_consistent():
         assert d.slot_mapping[i] == d.block_table[i, (n - 1) // 8] * 8 + (n - 1) % 8
     assert len(set(d.block_table[d.block_table > 0].tolist())) == int((d.block_table > 0).sum())  # disjoint pages
     assert workloads.prefill_flops([4], q_heads=1, head_dim=1) == 4 * 10
+
+
+def test_scheduler_plan_matches_the_oracle_plan():
+    """fg_scheduler_plan is host arithmetic: it runs without a GPU and must agree with the
+    restated reference heuristics on every field."""
+    import random
+
+    from oracle import reference_oracle as O
+
+    rng = random.Random(5)
+    for _ in range(3000):
+        hk = rng.choice([1, 2, 4, 8, 16])
+        hq = hk * rng.choice([1, 2, 4, 7, 8, 16])
+        d = rng.choice([32, 64, 72, 96, 128, 160, 192, 256])
+        dv = rng.choice([d, d, 64, 128, 256, 512])
+        args = (rng.choice([1, 2, 17, 128, 300, 992, 993, 100000]), rng.choice([1, 1, 2, 7, 64, 128, 500, 40000]),
+                rng.choice([16, 100, 512, 3000, 8192, 70000, 5000000]), hq, hk, d, dv)
+        kw = dict(page_size=rng.choice([None, None, 16, 64, 128, 256]), max_seqlen_k_new=rng.choice([0, 0, 3, 200]),
+                  is_causal=rng.random() < 0.5, window_size_left=rng.choice([-1, -1, 0, 100, 5000]),
+                  window_size_right=rng.choice([-1, -1, 0, 50]), has_softcap=rng.random() < 0.2,
+                  num_splits=rng.choice([0, 0, 0, 1, 2, 4, 300]), pack_gqa=rng.choice([None, None, True, False]),
+                  varlen_q=rng.random() < 0.3, has_leftpad=rng.random() < 0.2)
+        margin = rng.choice([0, 0, 8, 100])
+        a = fg.scheduler_plan(*args, sm_margin=margin, **kw)
+        b = O.scheduler_plan(*args, num_sm=148 - margin, **kw)
+        got = (a["num_splits"], bool(a["pack_gqa"]), a["block_m"], a["block_n"], bool(a["use_dynamic_split"]),
+               bool(a["is_causal"]), bool(a["is_local"]), a["q_per_kv"], a["heads"])
+        want = (b["num_splits"], b["pack_gqa"], b["block_m"], b["block_n"], b["dynamic"], b["causal"], b["local"],
+                b["q_per_kv"], b["heads"])
+        assert got == want, (args, margin, kw)
+        assert a["metadata_len"] == 1 + (args[0] if args[0] <= 992 else 0)
+    # argument errors of the reference (ops/get_scheduler_metadata.py:596-603) and the sm_100a-only rule
+    with pytest.raises(AssertionError, match="fp16 and bf16"):
+        fg.scheduler_plan(4, 1, 512, 8, 8, 128, 128, torch.float32)
+    with pytest.raises(AssertionError, match="must divide"):
+        fg.scheduler_plan(4, 1, 512, 9, 4, 128, 128)
+    with pytest.raises(RuntimeError, match="below 9.0"):
+        fg.scheduler_plan(4, 1, 512, 8, 8, 128, 128, arch=80)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        fg.get_scheduler_metadata(2, 1, 512, 8, 8, 128, 128, torch.bfloat16, torch.tensor([5, 9], dtype=torch.int32))

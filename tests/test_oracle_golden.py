@@ -85,3 +85,20 @@ def test_pointwise_and_blas_match_reference_oracle(golden_dir):
     torch.testing.assert_close(O.silu_and_mul(c["x"], c["y"]), c["silu_and_mul"], atol=0, rtol=0)
     torch.testing.assert_close(O.mm(c["a"], c["b"]), c["mm"], atol=0, rtol=0)
     torch.testing.assert_close(O.addmm(c["bias"], c["a"], c["b"], c["alpha"], c["beta"]), c["addmm"], atol=0, rtol=0)
+
+
+def _scheduler_kwargs(case):
+    kw = dict(case["kwargs"])
+    kw.pop("qkv_dtype")
+    kw.pop("cu_seqlens_k")  # accepted and never read by the reference
+    return kw
+
+
+def test_scheduler_metadata_matches_reference_run(golden_dir):
+    """The fixture holds the reference function's own results (its Triton kernels run under
+    the interpreter, device queries answered as a B200)."""
+    cases = _load(golden_dir, "golden_scheduler_metadata.pt")
+    assert len(cases) >= 150
+    for i, c in enumerate(cases):
+        got = O.get_scheduler_metadata(sm_count=c["sm_count"], **_scheduler_kwargs(c))
+        assert got.dtype == torch.int32 and torch.equal(got, c["metadata"]), i
