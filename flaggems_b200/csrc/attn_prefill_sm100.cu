@@ -28,9 +28,12 @@
 // P aliases the first 32 columns of its score buffer (keys [16k,16k+16) in columns 8k..8k+8).
 // Every wait in the kernel is an mbarrier wait with a time limit (no named barriers, no
 // register reallocation): a wait that gives up sets the device status word and the CTA drains.
-// The kernel is persistent: one CTA per SM keeps its shared memory, TMEM and tensor maps and
-// draws work items from a ticket counter (query blocks of a sequence from the longest causal
-// prefix to the shortest); between items the CTA synchronises and re-initialises its barriers.
+// The kernel is persistent: one CTA per SM keeps its shared memory, TMEM, tensor maps and barriers
+// and draws work items from a ticket counter (query blocks of a sequence from the longest causal
+// prefix to the shortest).  Nothing synchronises the CTA between items: the producer warp publishes
+// the next item through a two-slot ring and loads ahead, the roles follow the barrier phases with
+// running counters, and the first score steps of an item are computed while the previous output
+// tile is still being normalised and stored.
 //
 // Measured costs that shaped this layout (B200, SM clocks, microbenchmarks on an otherwise
 // idle SM): an mbarrier arrive reaches a waiting thread after 110-150; the first result of
@@ -134,7 +137,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   // launch quickly instead of letting every remaining CTA run into the same timeout
   // (one thread reads it so that the whole CTA takes the same decision).
   __shared__ int s_drain;
-  __shared__ int64_t s_item;
+  __shared__ int64_t s_items[2];   // ring of work items published by the producer warp
   if (threadIdx.x == 0) s_drain = *reinterpret_cast<volatile int*>(a.status);
   __syncthreads();
   if (s_drain != 0) return;
@@ -145,20 +148,40 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint8_t* sK = smem + 2 * TILE_BYTES;      // [2 stages]
   uint8_t* sV = smem + 4 * TILE_BYTES;      // [2 stages]
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
-  uint64_t* q_full = bars;            // [1]
-  uint64_t* k_full = bars + 1;        // [2]
-  uint64_t* k_empty = bars + 3;       // [2]
-  uint64_t* v_full = bars + 5;        // [2]
-  uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2 tiles][2 score buffers]
-  uint64_t* p_ready = bars + 13;      // [2 tiles][2 score buffers]
-  uint64_t* o_done = bars + 17;       // [2 tiles][2]: PV of even / odd steps (a softmax warp can be two
+  uint64_t* q_full = bars;            // [1]  Q tiles of an item have landed
+  uint64_t* q_empty = bars + 1;       // [1]  every QK of an item has been executed: Q may be overwritten
+  uint64_t* k_full = bars + 2;        // [2]
+  uint64_t* k_empty = bars + 4;       // [2]
+  uint64_t* v_full = bars + 6;        // [2]
+  uint64_t* v_empty = bars + 8;       // [2]
+  uint64_t* s_full = bars + 10;       // [2 tiles][2 score buffers]
+  uint64_t* p_ready = bars + 14;      // [2 tiles][2 score buffers]
+  uint64_t* o_done = bars + 18;       // [2 tiles][2]: PV of even / odd steps (a softmax warp can be two
                                       // steps ahead of the tensor pipe, one parity bit per barrier is not enough)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
+  uint64_t* o_free = bars + 22;       // [2 tiles] the output tile of the previous item has been read out
+  uint64_t* item_full = bars + 24;    // [2]
+  uint64_t* item_empty = bars + 26;   // [2]
+  constexpr int NUM_BARS = 28;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NUM_BARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    mbar_init(q_full, 1);
+    mbar_init(q_empty, NT);           // one commit per issuing thread
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], NT);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], NT);
+      mbar_init(&o_free[i], 4);       // one arrival per softmax warp of the tile
+      mbar_init(&item_full[i], 1);
+      mbar_init(&item_empty[i], 5 * NT);   // per tile: the issuing thread and four softmax warps
+    }
+    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
+    for (int i = 0; i < 4; ++i) mbar_init(&o_done[i], 1);
+    mbar_fence_init();
     prefetch_tmap(&tmap_q);
     prefetch_tmap(&tmap_k);
     prefetch_tmap(&tmap_v);
@@ -171,72 +194,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // ---- persistent loop: a CTA keeps its shared memory, TMEM and tensor maps and draws work items
-  // (query block x head pair x sequence; the heaviest query blocks of a sequence first) from a
-  // ticket counter.  Blocks beyond a sequence's end cost one counter increment instead of a CTA
-  // launch, and launch, allocation and descriptor fetch are paid once per SM, not once per item.
-  int n_done = 0;
-  for (;;) {
-    if (threadIdx.x == 0) s_item = (int64_t)atomicAdd(pa.ticket, 1u);
-    __syncthreads();
-    const int64_t item = s_item;
-    if (item >= pa.num_items) break;
-    const int m_block = pa.num_mb - 1 - (int)(item % pa.num_mb);
-    const int h0 = (int)((item / pa.num_mb) % pa.num_hp) * NT;
-    const int b = (int)(item / ((int64_t)pa.num_mb * pa.num_hp));
-    const SeqInfo s = seq_info(a, b);
-    const int m0 = m_block * BM;
-    if (m0 >= s.q_len) {
-      __syncthreads();   // everybody has read s_item
-      continue;
-    }
-    const int shift = s.k_len - s.q_len;
-    int vis = s.k_len;                  // keys visible to at least one row of this block
-    if (a.causal) vis = max(0, min(vis, m0 + BM + shift));
-    const int n_steps = (vis + STEP - 1) / STEP;
-    const int n_tiles = (n_steps + 1) / 2;   // K/V tiles of 128 keys
-#ifdef FG_PREFILL_TRACE
-    const bool trace_on = (item == 0) && (lane == 0);
-#endif
-  if (n_tiles == 0) {
-    // no visible key for any row of the block: zeros, lse = +inf
-    for (int idx = threadIdx.x; idx < NT * BM * (HD / 8); idx += NUM_THREADS) {
-      const int t = idx / (BM * (HD / 8));
-      const int r = (idx / (HD / 8)) % BM;
-      const int c = idx % (HD / 8);
-      if (m0 + r < s.q_len) {
-        uint4 z = make_uint4(0, 0, 0, 0);
-        char* o = reinterpret_cast<char*>(a.out) +
-                  ((int64_t)(s.q_begin + m0 + r) * a.o_rs + (int64_t)(h0 + t) * a.o_hs) * 2 + c * 16;
-        *reinterpret_cast<uint4*>(o) = z;
-      }
-    }
-    if (a.lse)
-      for (int idx = threadIdx.x; idx < NT * BM; idx += NUM_THREADS) {
-        const int t = idx / BM, r = idx % BM;
-        if (m0 + r < s.q_len) a.lse[(int64_t)(h0 + t) * a.total_q + s.q_begin + m0 + r] = INFINITY;
-      }
-    __syncthreads();
-    continue;
-  }
-
-  if (threadIdx.x == 0) {
-    if (n_done > 0)
-      for (int i = 0; i < 21; ++i) mbar_inval(&bars[i]);
-    mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], NT);   // one commit per issuing thread
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], NT);
-    }
-    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
-    for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
-    for (int i = 0; i < 4; ++i) mbar_init(&o_done[i], 1);
-    mbar_fence_init();
-  }
-  __syncthreads();
-  const int hk = h0 / a.group;
   const int st_code = kStatusAttnTimeout;
   // Every wait of a warp is polled by lane 0 and its outcome broadcast, so that a wait
   // that gave up takes the whole warp the same way.
@@ -246,48 +203,108 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     return __shfl_sync(0xffffffffu, r, 0) != 0;
   };
 
+  // ---- persistent roles.  The CTA keeps its shared memory, TMEM, tensor maps and barriers for
+  // the whole launch; the barriers are initialised once and every role follows their phases with
+  // running counters (work items, K/V tiles, score steps), so nothing synchronises the CTA between
+  // items: the producer warp draws the next item from the launch's ticket counter while the current
+  // one is still being computed, publishes it through a two-slot ring and loads its Q and first K/V
+  // tiles as soon as the stages are free; the issuing threads compute its first two score steps
+  // while the softmax warps still normalise and store the previous output.
+  struct Item {
+    int m0, h0, b, n_steps, n_tiles, shift;
+    SeqInfo s;
+  };
+  auto decode = [&](int64_t item, Item& it) {
+    const int m_block = pa.num_mb - 1 - (int)(item % pa.num_mb);   // heaviest query block of a sequence first
+    it.h0 = (int)((item / pa.num_mb) % pa.num_hp) * NT;
+    it.b = (int)(item / ((int64_t)pa.num_mb * pa.num_hp));
+    it.s = seq_info(a, it.b);
+    it.m0 = m_block * BM;
+    it.shift = it.s.k_len - it.s.q_len;
+    int vis = it.s.k_len;               // keys visible to at least one row of this block
+    if (a.causal) vis = max(0, min(vis, it.m0 + BM + it.shift));
+    it.n_steps = (vis + STEP - 1) / STEP;
+    it.n_tiles = (it.n_steps + 1) / 2;  // K/V tiles of 128 keys
+  };
+  // Next published item of a consumer role (lane 0 of a warp, or a single thread): -1 when the
+  // launch has no more work or a wait gave up.
+  auto next_item = [&](uint32_t n) -> int64_t {
+    if (!mbar_wait(&item_full[n & 1], (n >> 1) & 1, abort_flag, a.status, FG_SITE(20))) return -1;
+    const int64_t item = s_items[n & 1];
+    mbar_arrive(&item_empty[n & 1]);
+    return item;
+  };
+
   if (warp == TMA_WARP) {
     // ================================ TMA producer ================================
-    if (lane == 0) {
-      mbar_expect_tx(q_full, NT * TILE_BYTES);
-      for (int t = 0; t < NT; ++t)
-        for (int hf = 0; hf < 2; ++hf)
-          tma_load_3d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmap_q, q_full, hf * 64, h0 + t, s.q_begin + m0);
-    }
-    const int32_t* bt_row = a.paged ? a.block_table + (int64_t)b * a.bt_stride : nullptr;
-    const int last_page = a.paged ? max(0, (s.k_len - 1) / a.block_size) : 0;
+    uint32_t n_pub = 0, n_q = 0, kv = 0;   // items published, items with a Q load, K/V tiles loaded
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int stg = j & 1;
-      const uint32_t ph = (uint32_t)((j >> 1) & 1);
-      // page of this lane (paged form): lanes [0, pages_per_tile) each fetch one page
-      int page = 0, row_off = 0;
-      if (a.paged && lane < pa.pages_per_tile) {
-        const int tok = j * BN + lane * pa.page_rows;
-        int pg = tok / a.block_size;
-        row_off = tok - pg * a.block_size;
-        pg = min(pg, last_page);  // pages past the end of the sequence: refetch a valid one (masked later)
-        page = max(0, min(bt_row[pg], a.num_blocks - 1));
-      }
-      for (int which = 0; which < 2 && ok; ++which) {
-        uint64_t* full = which ? &v_full[stg] : &k_full[stg];
-        uint64_t* empty = which ? &v_empty[stg] : &k_empty[stg];
-        const CUtensorMap* tm = which ? &tmap_v : &tmap_k;
-        uint8_t* dst = (which ? sV : sK) + stg * TILE_BYTES;
-        if (!wwait(empty, ph ^ 1, 1 + which)) {
-          ok = false;
+    while (ok) {
+      // draw tickets until one names a query block inside its sequence
+      Item it;
+      int64_t item = 0;
+      for (;;) {
+        if (lane == 0) item = (int64_t)atomicAdd(pa.ticket, 1u);
+        item = __shfl_sync(0xffffffffu, item, 0);
+        if (item >= pa.num_items) {
+          item = -1;
           break;
         }
-        if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
-        __syncwarp();
-        if (a.paged) {
-          if (lane < pa.pages_per_tile) {
-            for (int hf = 0; hf < 2; ++hf)
-              tma_load_4d(dst + hf * HALF_BYTES + lane * pa.page_rows * 128, tm, full, hf * 64, hk, row_off, page);
-          }
-        } else if (lane == 0) {
+        decode(item, it);
+        if (it.m0 < it.s.q_len) break;
+      }
+      if (!wwait(&item_empty[n_pub & 1], ((n_pub >> 1) & 1) ^ 1, 21)) break;
+      if (lane == 0) {
+        s_items[n_pub & 1] = item;
+        mbar_arrive(&item_full[n_pub & 1]);   // release: the slot is written before the arrival is seen
+      }
+      ++n_pub;
+      if (item < 0) break;
+      if (it.n_tiles == 0) continue;          // no visible key: the softmax warps write zeros
+      const SeqInfo& s = it.s;
+      const int hk = it.h0 / a.group;
+      if (n_q > 0 && !wwait(q_empty, (n_q - 1) & 1, 22)) break;
+      if (lane == 0) {
+        mbar_expect_tx(q_full, NT * TILE_BYTES);
+        for (int t = 0; t < NT; ++t)
           for (int hf = 0; hf < 2; ++hf)
-            tma_load_3d(dst + hf * HALF_BYTES, tm, full, hf * 64, hk, s.k_begin + j * BN);
+            tma_load_3d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmap_q, q_full, hf * 64, it.h0 + t, s.q_begin + it.m0);
+      }
+      ++n_q;
+      const int32_t* bt_row = a.paged ? a.block_table + (int64_t)it.b * a.bt_stride : nullptr;
+      const int last_page = a.paged ? max(0, (s.k_len - 1) / a.block_size) : 0;
+      for (int j = 0; j < it.n_tiles && ok; ++j, ++kv) {
+        const int stg = kv & 1;
+        const uint32_t ph = (kv >> 1) & 1;
+        // page of this lane (paged form): lanes [0, pages_per_tile) each fetch one page
+        int page = 0, row_off = 0;
+        if (a.paged && lane < pa.pages_per_tile) {
+          const int tok = j * BN + lane * pa.page_rows;
+          int pg = tok / a.block_size;
+          row_off = tok - pg * a.block_size;
+          pg = min(pg, last_page);  // pages past the end of the sequence: refetch a valid one (masked later)
+          page = max(0, min(bt_row[pg], a.num_blocks - 1));
+        }
+        for (int which = 0; which < 2 && ok; ++which) {
+          uint64_t* full = which ? &v_full[stg] : &k_full[stg];
+          uint64_t* empty = which ? &v_empty[stg] : &k_empty[stg];
+          const CUtensorMap* tm = which ? &tmap_v : &tmap_k;
+          uint8_t* dst = (which ? sV : sK) + stg * TILE_BYTES;
+          if (!wwait(empty, ph ^ 1, 1 + which)) {
+            ok = false;
+            break;
+          }
+          if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
+          __syncwarp();
+          if (a.paged) {
+            if (lane < pa.pages_per_tile) {
+              for (int hf = 0; hf < 2; ++hf)
+                tma_load_4d(dst + hf * HALF_BYTES + lane * pa.page_rows * 128, tm, full, hf * 64, hk, row_off, page);
+            }
+          } else if (lane == 0) {
+            for (int hf = 0; hf < 2; ++hf)
+              tma_load_3d(dst + hf * HALF_BYTES, tm, full, hf * 64, hk, s.k_begin + j * BN);
+          }
         }
       }
     }
@@ -308,42 +325,70 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       const uint32_t k_lo0 = (uint32_t)umma_desc_sw128(smem_u32(sK), 0, 1024);
       const uint32_t v_lo0 = (uint32_t)umma_desc_sw128(smem_u32(sV), HALF_BYTES, 1024);
       const uint32_t s_tmem = tmem_base + t * 128, o_tmem = tmem_base + 256 + t * 128;
+      uint32_t n_it = 0, n_q = 0, kv0 = 0, g0 = 0;   // items read, items computed, K/V tiles and score steps before this item
       bool ok = true;
-      // scores of step i: keys [64 i, 64 i + 64) = rows (i & 1) * 64 .. of K tile i >> 1
-      auto issue_qk = [&](int i) {
-        const int tile = i >> 1, stg = tile & 1;
-        if (!(i & 1) && !mbar_wait(&k_full[stg], (uint32_t)((tile >> 1) & 1), abort_flag, a.status, FG_SITE(8))) {
-          ok = false;
-          return;
-        }
-        tc_fence_after();
-        const uint32_t k_lo = k_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (STEP * 128 >> 4);
+      while (ok) {
+        const int64_t item = next_item(n_it++);
+        if (item < 0) break;
+        Item it;
+        decode(item, it);
+        const int n_steps = it.n_steps;
+        if (n_steps == 0) continue;
+#ifdef FG_PREFILL_TRACE
+        const bool trace_on = item == 0;
+#endif
+        // scores of step i of this item: keys [64 i, 64 i + 64) = rows (i & 1) * 64 .. of its K tile i >> 1;
+        // score buffer and barrier phases follow the running step count g0 + i
+        auto issue_qk = [&](int i) {
+          const uint32_t tile = kv0 + (uint32_t)(i >> 1), stg = tile & 1, g = g0 + (uint32_t)i;
+          if (!(i & 1) && !mbar_wait(&k_full[stg], (tile >> 1) & 1, abort_flag, a.status, FG_SITE(8))) {
+            ok = false;
+            return;
+          }
+          tc_fence_after();
+          const uint32_t k_lo = k_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (STEP * 128 >> 4);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
-          const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
-          mma_f16_ss_lohi(s_tmem + (i & 1) * STEP, q_lo + off, k_lo + off, desc_hi, idesc_qk, k != 0 ? 1u : 0u);
-        }
-        tc_commit(&s_full[t * 2 + (i & 1)]);
-        FG_TRACE(48 + t, i);
-        if ((i & 1) || i == n_steps - 1) tc_commit(&k_empty[stg]);   // last step on this K tile
-      };
-      ok = mbar_wait(q_full, 0, abort_flag, a.status, FG_SITE(3));
-      if (ok) issue_qk(0);
-      if (ok && n_steps > 1) issue_qk(1);
-      for (int i = 0; i < n_steps && ok; ++i) {
-        const int tile = i >> 1, stg = tile & 1;
-        if (!(i & 1) && !mbar_wait(&v_full[stg], (uint32_t)((tile >> 1) & 1), abort_flag, a.status, FG_SITE(5))) break;
-        if (!mbar_wait(&p_ready[t * 2 + (i & 1)], (uint32_t)((i >> 1) & 1), abort_flag, a.status, FG_SITE(6))) break;
-        tc_fence_after();
-        FG_TRACE(0 + t, i);
-        const uint32_t v_lo = v_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (4 * 2048 >> 4);
-        const uint32_t p_tmem = s_tmem + (i & 1) * STEP;
+          for (int k = 0; k < HD / 16; ++k) {
+            const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+            mma_f16_ss_lohi(s_tmem + (g & 1) * STEP, q_lo + off, k_lo + off, desc_hi, idesc_qk, k != 0 ? 1u : 0u);
+          }
+          tc_commit(&s_full[t * 2 + (g & 1)]);
+          FG_TRACE(48 + t, i);
+          if ((i & 1) || i == n_steps - 1) tc_commit(&k_empty[stg]);   // last step on this K tile
+          if (i == n_steps - 1) tc_commit(q_empty);                    // last use of this item's Q
+        };
+        if (!mbar_wait(q_full, n_q & 1, abort_flag, a.status, FG_SITE(3))) break;
+        issue_qk(0);
+        if (ok && n_steps > 1) issue_qk(1);
+        for (int i = 0; i < n_steps && ok; ++i) {
+          const uint32_t tile = kv0 + (uint32_t)(i >> 1), stg = tile & 1, g = g0 + (uint32_t)i;
+          if (!(i & 1) && !mbar_wait(&v_full[stg], (tile >> 1) & 1, abort_flag, a.status, FG_SITE(5))) {
+            ok = false;
+            break;
+          }
+          if (!mbar_wait(&p_ready[t * 2 + (g & 1)], (g >> 1) & 1, abort_flag, a.status, FG_SITE(6))) {
+            ok = false;
+            break;
+          }
+          // the first PV of an item overwrites the output tile: the previous one must have been read out
+          if (i == 0 && n_q > 0 && !mbar_wait(&o_free[t], (n_q - 1) & 1, abort_flag, a.status, FG_SITE(7))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          FG_TRACE(0 + t, i);
+          const uint32_t v_lo = v_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (4 * 2048 >> 4);
+          const uint32_t p_tmem = s_tmem + (g & 1) * STEP;
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          mma_f16_ts_lohi(o_tmem, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&o_done[t * 2 + (i & 1)]);
-        if ((i & 1) || i == n_steps - 1) tc_commit(&v_empty[stg]);     // last step on this V tile
-        if (i + 2 < n_steps) issue_qk(i + 2);
+          for (int k = 0; k < 4; ++k)
+            mma_f16_ts_lohi(o_tmem, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&o_done[t * 2 + (g & 1)]);
+          if ((i & 1) || i == n_steps - 1) tc_commit(&v_empty[stg]);     // last step on this V tile
+          if (i + 2 < n_steps) issue_qk(i + 2);
+        }
+        ++n_q;
+        kv0 += (uint32_t)it.n_tiles;
+        g0 += (uint32_t)n_steps;
       }
     }
   } else if (warp < 4 * NT) {
@@ -351,156 +396,187 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
     const int t = warp >> 2;                  // Q tile
     const int quarter = warp & 3;             // TMEM lane quarter this warp may touch
     const int r = quarter * 32 + lane;        // row inside the tile == TMEM lane
-    const int qpos = m0 + r;                  // query position inside the sequence
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_addr + t * 128;         // my row of the score tile
     const uint32_t o_addr = tmem_base + lane_addr + 256 + t * 128;   // my row of the output tile
     constexpr bool bf16 = kBf16;
     const float scale = a.scale_log2;
-    float m_used = -INFINITY, l_run = 0.f;
+    uint32_t n_it = 0, kv0 = 0, g0 = 0;       // items read, K/V tiles and score steps before this item
     bool ok = true;
 
-    for (int i = 0; i < n_steps; ++i) {
-      const int sb = i & 1;                              // score buffer of this step
-      const uint32_t sb_addr = s_addr + sb * STEP;
-      if (!wwait(&s_full[t * 2 + sb], (uint32_t)((i >> 1) & 1), 10)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
-      if (quarter == 0) FG_TRACE(4 + t * 16, i);
-      float sv[64];
-      tmem_ld32(sb_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      tmem_ld32(sb_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      tmem_ld_wait();
-      const int col0 = i * STEP;
-      if ((col0 + STEP > s.k_len) || (a.causal && (col0 + STEP - 1 > m0 + shift))) {
-        int lim = s.k_len - 1;                         // last visible column of this row
-        if (a.causal) lim = min(lim, qpos + shift);
+    while (ok) {
+      int64_t item = 0;
+      if (lane == 0) item = next_item(n_it);
+      ++n_it;
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (item < 0) break;
+      Item it;
+      decode(item, it);
+      const SeqInfo& s = it.s;
+      const int m0 = it.m0, shift = it.shift, n_steps = it.n_steps;
+      const int qpos = m0 + r;                  // query position inside the sequence
+      const bool valid = qpos < s.q_len;
+      char* orow = reinterpret_cast<char*>(a.out) +
+                   ((int64_t)(s.q_begin + qpos) * a.o_rs + (int64_t)(it.h0 + t) * a.o_hs) * 2;
+      float* lse_ptr = a.lse ? a.lse + (int64_t)(it.h0 + t) * a.total_q + s.q_begin + qpos : nullptr;
+#ifdef FG_PREFILL_TRACE
+      const bool trace_on = (item == 0) && (lane == 0);
+#endif
+      if (n_steps == 0) {
+        // no visible key for any row of the block: zeros, lse = +inf
+        if (valid) {
 #pragma unroll
-        for (int e = 0; e < 64; ++e)
-          if (col0 + e > lim) sv[e] = -INFINITY;
-      }
-      float m4[4] = {sv[0], sv[1], sv[2], sv[3]};
-#pragma unroll
-      for (int e = 4; e < 64; e += 8) {
-        m4[0] = max3(m4[0], sv[e], sv[e + 1]);
-        m4[1] = max3(m4[1], sv[e + 2], sv[e + 3]);
-        if (e + 4 < 64) {
-          m4[2] = max3(m4[2], sv[e + 4], sv[e + 5]);
-          m4[3] = max3(m4[3], sv[e + 6], sv[e + 7]);
+          for (int c = 0; c < HD / 8; ++c) *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(0, 0, 0, 0);
+          if (lse_ptr) *lse_ptr = INFINITY;
         }
+        continue;
       }
-      const float m_tile = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]) * scale;  // scale > 0; -inf stays -inf
-      if (quarter == 0) FG_TRACE(6 + t * 16, i);
-      // Raise the reference maximum only when it grows by more than the threshold:
-      // probabilities then stay below 2^8 and the accumulator needs no rescale.
-      const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
-      if (i > 0 && __any_sync(0xffffffffu, raise)) {
-        // every PV issued so far (steps 0 .. i-1; the pipe completes them in order) must have
-        // landed before O is touched
-        if (!wwait(&o_done[t * 2 + ((i - 1) & 1)], (uint32_t)(((i - 1) >> 1) & 1), 14)) {
+      float m_used = -INFINITY, l_run = 0.f;
+
+      for (int i = 0; i < n_steps; ++i) {
+        const uint32_t g = g0 + (uint32_t)i;
+        const int sb = (int)(g & 1);                       // score buffer of this step
+        const uint32_t sb_addr = s_addr + sb * STEP;
+        if (!wwait(&s_full[t * 2 + sb], (g >> 1) & 1, 10)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const float f = raise ? ex2(m_used - m_tile) : 1.0f;  // m_used == -inf -> 0 (accumulator is 0 there)
+        if (quarter == 0) FG_TRACE(4 + t * 16, i);
+        float sv[64];
+        tmem_ld32(sb_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld32(sb_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_ld_wait();
+        const int col0 = i * STEP;
+        if ((col0 + STEP > s.k_len) || (a.causal && (col0 + STEP - 1 > m0 + shift))) {
+          int lim = s.k_len - 1;                         // last visible column of this row
+          if (a.causal) lim = min(lim, qpos + shift);
+#pragma unroll
+          for (int e = 0; e < 64; ++e)
+            if (col0 + e > lim) sv[e] = -INFINITY;
+        }
+        float m4[4] = {sv[0], sv[1], sv[2], sv[3]};
+#pragma unroll
+        for (int e = 4; e < 64; e += 8) {
+          m4[0] = max3(m4[0], sv[e], sv[e + 1]);
+          m4[1] = max3(m4[1], sv[e + 2], sv[e + 3]);
+          if (e + 4 < 64) {
+            m4[2] = max3(m4[2], sv[e + 4], sv[e + 5]);
+            m4[3] = max3(m4[3], sv[e + 6], sv[e + 7]);
+          }
+        }
+        const float m_tile = fmaxf(max3(m4[0], m4[1], m4[2]), m4[3]) * scale;  // scale > 0; -inf stays -inf
+        if (quarter == 0) FG_TRACE(6 + t * 16, i);
+        // Raise the reference maximum only when it grows by more than the threshold:
+        // probabilities then stay below 2^8 and the accumulator needs no rescale.
+        const bool raise = m_tile > m_used + kRescaleThreshold || (m_used == -INFINITY && m_tile > -INFINITY);
+        if (i > 0 && __any_sync(0xffffffffu, raise)) {
+          // every PV issued so far (steps 0 .. i-1; the pipe completes them in order) must have
+          // landed before O is touched
+          if (!wwait(&o_done[t * 2 + ((g - 1) & 1)], ((g - 1) >> 1) & 1, 14)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const float f = raise ? ex2(m_used - m_tile) : 1.0f;  // m_used == -inf -> 0 (accumulator is 0 there)
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t o[32];
-          tmem_ld32(o_addr + c * 32, o);
-          tmem_ld_wait();
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
-          tmem_st32(o_addr + c * 32, o);
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * f);
+            tmem_st32(o_addr + c * 32, o);
+          }
+          l_run *= f;
         }
-        l_run *= f;
-      }
-      if (raise) m_used = m_tile;
-      const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
-      if (a.paged && i == n_steps - 1 && col0 + STEP > s.k_len) {
-        // Rows of the last V tile past the end of the sequence hold whatever the cache
-        // page holds; zero the ones this step multiplies so 0 * garbage can never produce
-        // NaN.  Each Q tile does it for itself (same zeros twice): its PV is ordered after
-        // its own softmax only.
-        const int tile = i >> 1, stg = tile & 1;
-        if (!wwait(&v_full[stg], (uint32_t)((tile >> 1) & 1), 15)) {
-          ok = false;
-          break;
+        if (raise) m_used = m_tile;
+        const float neg_m = m_used == -INFINITY ? 0.f : -m_used;
+        if (a.paged && i == n_steps - 1 && col0 + STEP > s.k_len) {
+          // Rows of the last V tile past the end of the sequence hold whatever the cache
+          // page holds; zero the ones this step multiplies so 0 * garbage can never produce
+          // NaN.  Each Q tile does it for itself (same zeros twice): its PV is ordered after
+          // its own softmax only.
+          const int tl = i >> 1;
+          const uint32_t tile = kv0 + (uint32_t)tl, stg = tile & 1;
+          if (!wwait(&v_full[stg], (tile >> 1) & 1, 15)) {
+            ok = false;
+            break;
+          }
+          const int first = s.k_len - tl * BN;               // first invalid row of the tile
+          const int end = (i & 1) * STEP + STEP;             // this step's rows end here
+          uint8_t* vt = sV + stg * TILE_BYTES;
+          for (int idx = r; idx < (end - first) * 16; idx += 128) {
+            const int row = first + idx / 16, ch = idx % 16;
+            *reinterpret_cast<uint4*>(vt + (ch >> 3) * HALF_BYTES + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
         }
-        const int first = s.k_len - tile * BN;             // first invalid row of the tile
-        const int end = (i & 1) * STEP + STEP;             // this step's rows end here
-        uint8_t* vt = sV + stg * TILE_BYTES;
-        for (int idx = r; idx < (end - first) * 16; idx += 128) {
-          const int row = first + idx / 16, ch = idx % 16;
-          *reinterpret_cast<uint4*>(vt + (ch >> 3) * HALF_BYTES + row * 128 + (ch & 7) * 16) = make_uint4(0, 0, 0, 0);
-        }
-        fence_proxy_async_smem();
-      }
-      // ---- probabilities -> 32 packed 32-bit columns over the start of the score buffer
-      // (the scores are all in registers, so P may overwrite them in TMEM)
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // ---- probabilities -> 32 packed 32-bit columns over the start of the score buffer
+        // (the scores are all in registers, so P may overwrite them in TMEM)
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        uint32_t pk[16];
+        for (int q = 0; q < 2; ++q) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int e = 0; e < 16; ++e) {
-          const float p0 = ex2(fmaf(sv[q * 32 + 2 * e], scale, neg_m));
-          const float p1 = ex2(fmaf(sv[q * 32 + 2 * e + 1], scale, neg_m));
-          sum4[e & 3] += p0 + p1;
-          pk[e] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
+          for (int e = 0; e < 16; ++e) {
+            const float p0 = ex2(fmaf(sv[q * 32 + 2 * e], scale, neg_m));
+            const float p1 = ex2(fmaf(sv[q * 32 + 2 * e + 1], scale, neg_m));
+            sum4[e & 3] += p0 + p1;
+            pk[e] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
+          }
+          tmem_st16(sb_addr + q * 16, pk);
         }
-        tmem_st16(sb_addr + q * 16, pk);
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (quarter == 0) FG_TRACE(40 + t * 8, i);
+        if (lane == 0) mbar_arrive(&p_ready[t * 2 + sb]);
       }
-      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (quarter == 0) FG_TRACE(40 + t * 8, i);
-      if (lane == 0) mbar_arrive(&p_ready[t * 2 + sb]);
-    }
+      if (!ok) break;
 
-    // ---- epilogue: normalise my row of O and write it out
-    if (ok && wwait(&o_done[t * 2 + ((n_steps - 1) & 1)], (uint32_t)(((n_steps - 1) >> 1) & 1), 16)) {
+      // ---- epilogue: normalise my row of O and write it out
+      const uint32_t g_last = g0 + (uint32_t)n_steps - 1;
+      if (!wwait(&o_done[t * 2 + (g_last & 1)], (g_last >> 1) & 1, 16)) break;
       tc_fence_after();
       const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-      const bool valid = qpos < s.q_len;
-      char* orow = reinterpret_cast<char*>(a.out) +
-                   ((int64_t)(s.q_begin + qpos) * a.o_rs + (int64_t)(h0 + t) * a.o_hs) * 2;
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t o[32];
         tmem_ld32(o_addr + c * 32, o);
         tmem_ld_wait();
+        if (c == 3) {
+          // my row of the output tile is in registers: once the four warps of the tile have said
+          // so, the next item's first PV may overwrite it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&o_free[t]);
+        }
         if (valid) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
             uint4 w;
             uint32_t* wp = reinterpret_cast<uint32_t*>(&w);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float x0 = __uint_as_float(o[q4 * 8 + 2 * i]) * inv;
-              const float x1 = __uint_as_float(o[q4 * 8 + 2 * i + 1]) * inv;
-              wp[i] = bf16 ? pack_bf16(x0, x1) : pack_f16(x0, x1);
+            for (int j = 0; j < 4; ++j) {
+              const float x0 = __uint_as_float(o[q4 * 8 + 2 * j]) * inv;
+              const float x1 = __uint_as_float(o[q4 * 8 + 2 * j + 1]) * inv;
+              wp[j] = bf16 ? pack_bf16(x0, x1) : pack_f16(x0, x1);
             }
             *reinterpret_cast<uint4*>(orow + c * 64 + q4 * 16) = w;
           }
         }
       }
-      if (valid && a.lse)
-        a.lse[(int64_t)(h0 + t) * a.total_q + s.q_begin + qpos] =
-            l_run > 0.f ? m_used * 0.6931471805599453f + logf(l_run) : INFINITY;
+      if (valid && lse_ptr) *lse_ptr = l_run > 0.f ? m_used * 0.6931471805599453f + logf(l_run) : INFINITY;
+      kv0 += (uint32_t)it.n_tiles;
+      g0 += (uint32_t)n_steps;
     }
   }
 
-    // ---- end of the item: every role has left its loop, every MMA and copy has been waited for
-    tc_fence_before();
-    __syncthreads();
-    ++n_done;
-    if (*abort_flag) break;
-  }
-
   // ================================ teardown ======================================
+  // Every role has left its loop: all MMAs and copies it issued have been waited for by the
+  // role that consumes them (the last output tile was read after its o_done barrier).
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP0) {
