@@ -335,7 +335,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         const int n_steps = it.n_steps;
         if (n_steps == 0) continue;
 #ifdef FG_PREFILL_TRACE
-        const bool trace_on = item == 0;
+        const bool trace_on = blockIdx.x == 0 && g0 == 0;   // the first item this CTA computes
 #endif
         // scores of step i of this item: keys [64 i, 64 i + 64) = rows (i & 1) * 64 .. of its K tile i >> 1;
         // score buffer and barrier phases follow the running step count g0 + i
@@ -420,7 +420,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
                    ((int64_t)(s.q_begin + qpos) * a.o_rs + (int64_t)(it.h0 + t) * a.o_hs) * 2;
       float* lse_ptr = a.lse ? a.lse + (int64_t)(it.h0 + t) * a.total_q + s.q_begin + qpos : nullptr;
 #ifdef FG_PREFILL_TRACE
-      const bool trace_on = (item == 0) && (lane == 0);
+      const bool trace_on = blockIdx.x == 0 && g0 == 0 && lane == 0;
 #endif
       if (n_steps == 0) {
         // no visible key for any row of the block: zeros, lse = +inf
@@ -437,6 +437,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         const uint32_t g = g0 + (uint32_t)i;
         const int sb = (int)(g & 1);                       // score buffer of this step
         const uint32_t sb_addr = s_addr + sb * STEP;
+        if (quarter == 0) FG_TRACE(8 + t * 16, i);
         if (!wwait(&s_full[t * 2 + sb], (g >> 1) & 1, 10)) {
           ok = false;
           break;
@@ -531,7 +532,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (quarter == 0) FG_TRACE(40 + t * 8, i);
+        if (quarter == 0) FG_TRACE(56 + t, i);
         if (lane == 0) mbar_arrive(&p_ready[t * 2 + sb]);
       }
       if (!ok) break;
