@@ -382,9 +382,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             mma_f16_ts_lohi(o_tmem, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+          // The next scores are what the softmax warps wait for: they and their commit go first.  The
+          // commits below then also cover those score MMAs, i.e. "PV done" and "V stage free" are
+          // announced about 500 clocks later than they could be; the first is waited for only on a
+          // rescale and at the end of the item, the second has a whole K/V tile of slack.
+          if (i + 2 < n_steps) issue_qk(i + 2);
           tc_commit(&o_done[t * 2 + (g & 1)]);
           if ((i & 1) || i == n_steps - 1) tc_commit(&v_empty[stg]);     // last step on this V tile
-          if (i + 2 < n_steps) issue_qk(i + 2);
         }
         ++n_q;
         kv0 += (uint32_t)it.n_tiles;
