@@ -174,13 +174,14 @@ class Step:
     """The operators of one step with their inputs resident on ``device``."""
 
     def __init__(self, device, rank: int, world: int, seed: int = 0, small: bool = False, only: str = "",
-                 gather: str = "p2p", row_blocks: int = 1):
+                 gather: str = "p2p", row_blocks: int = 1, op_order: str = "spread"):
         import flaggems_b200 as fg
         from flaggems_b200 import dist as fdist
         from flaggems_b200 import workloads as W
 
         self.gather = gather
         self.row_blocks = row_blocks
+        self.op_order = op_order
         self.skip_gather = False   # N > 1: second timing of the step without the all-gathers
 
         self.fg, self.W, self.fdist = fg, W, fdist
@@ -237,33 +238,44 @@ class Step:
                 ops.append((f"addmm[{name}]", self._gemm_call(name, True), M * N * (2 * K + 1), "tensor"))
             else:
                 ops.append((f"mm[{name}]", self._gemm_call(name, False), 2 * M * N * K, "tensor"))
-        ops.append(("fused_add_rms_norm", lambda: fg.fused_add_rms_norm(self.x, self.res, [H], self.w, self.eps),
+        rest = {}
+        rest["fused_add_rms_norm"] = (("fused_add_rms_norm", lambda: fg.fused_add_rms_norm(self.x, self.res, [H], self.w, self.eps),
                     4 * T * H * 2 + H * 2, "hbm"))
         tq, hq, d = self.q.shape
         hk = self.k.shape[1]
-        ops.append(("rotary_embedding",
+        rest["rotary_embedding"] = (("rotary_embedding",
                     lambda: fg.apply_rotary_pos_emb(self.q, self.k, self.cos, self.sin, self.pos, False, True),
                     2 * (tq * hq * d + tq * hk * d) * 2 + tq * 2 * (d // 2) * 2 + tq * 8, "hbm"))
         a1, a2 = self.act[:, :self.half], self.act[:, self.half:]
-        ops.append(("silu_and_mul", lambda: fg.silu_and_mul_out(a1, a2, self.silu_out),
+        rest["silu_and_mul"] = (("silu_and_mul", lambda: fg.silu_and_mul_out(a1, a2, self.silu_out),
                     self.act.numel() * 2 + self.silu_out.numel() * 2, "hbm"))
         p = self.pre
-        ops.append(("flash_attn_varlen_func[prefill]",
+        rest["prefill"] = (("flash_attn_varlen_func[prefill]",
                     lambda: fg.flash_attn_varlen_func(p.q, p.key_cache, p.value_cache, p.max_seqlen_q, p.cu_seqlens_q,
                                                       p.max_seqlen_k, seqused_k=p.seqused_k, causal=True,
                                                       block_table=p.block_table, out=self.pre_out),
                     W.prefill_flops(p.query_lens), "tensor"))
         dd = self.dec
         nk = dd.new_key.numel() * 2
-        ops.append(("reshape_and_cache_flash",
+        rest["cache"] = (("reshape_and_cache_flash",
                     lambda: fg.reshape_and_cache_flash(dd.new_key, dd.new_value, dd.key_cache, dd.value_cache,
                                                        dd.slot_mapping, "auto", None, None),
                     4 * nk + dd.slot_mapping.numel() * 8, "hbm"))
-        ops.append(("flash_attn_varlen_func[decode]",
+        rest["decode"] = (("flash_attn_varlen_func[decode]",
                     lambda: fg.flash_attn_varlen_func(dd.q, dd.key_cache, dd.value_cache, 1, dd.cu_seqlens_q,
                                                       dd.max_seqlen_k, seqused_k=dd.seqused_k, causal=True,
                                                       block_table=dd.block_table, out=self.dec_out),
                     W.decode_bytes(dd.kv_lens, len(dd.kv_lens)), "hbm"))
+        # Order of the remaining operators.  The calls are independent (own buffers), so any order computes
+        # the same; what the order changes is whose time the write-back of an operator's output is counted
+        # in: up to 126 MB of dirty L2 lines leave for DRAM while the NEXT operator runs.  A tensor-bound
+        # operator absorbs that, a 20 us streaming kernel doubles its DRAM traffic.  The short memory-bound
+        # operators therefore follow the operators that leave the L2 cleanest (--op-order grouped restores the
+        # order by operator family that earlier lines of this benchmark used).
+        order = (["prefill", "fused_add_rms_norm", "cache", "decode", "rotary_embedding", "silu_and_mul"]
+                 if self.op_order == "spread" else
+                 ["fused_add_rms_norm", "rotary_embedding", "silu_and_mul", "prefill", "cache", "decode"])
+        ops += [rest[k] for k in order]
         if self.only:
             ops = [o for o in ops if self.only in o[0]]
             if not ops:
@@ -694,6 +706,9 @@ def main():
                          "buffers closed by one NCCL all-reduce, or ncclAllGather)")
     ap.add_argument("--row-blocks", type=int, default=1,
                     help="N > 1 with --gather p2p: row blocks a projection is computed and pushed in")
+    ap.add_argument("--op-order", default="spread", choices=["spread", "grouped"],
+                    help="order of the operators inside a step: 'spread' puts the short memory-bound operators "
+                         "behind the ones that leave little dirty data in L2, 'grouped' runs them by family")
     ap.add_argument("--small", action="store_true",
                     help="reduced attention / GEMM sizes (for profiler captures); not a benchmark configuration")
     args = ap.parse_args()
@@ -733,7 +748,8 @@ def main():
     if world > 1 and args.gather == "nccl":
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         _lib.set_num_sms(sms - NCCL_CTAS)
-    step = Step(device, rank, world, small=args.small, only=args.only, gather=args.gather, row_blocks=args.row_blocks)
+    step = Step(device, rank, world, small=args.small, only=args.only, gather=args.gather, row_blocks=args.row_blocks,
+                op_order=args.op_order)
     n_ops = len(step.ops)
 
     def barrier():
@@ -818,7 +834,8 @@ def main():
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic", "config": workload_config(world, n_ops, args.small, args.only), "roofline": roofline,
+        "data": "synthetic", "config": dict(workload_config(world, n_ops, args.small, args.only),
+                                            op_order=[o[0] for o in step.ops]), "roofline": roofline,
         "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches), "clocks": clocks, "per_op": per_op, "device_status": status,
