@@ -249,28 +249,66 @@ __global__ void __launch_bounds__(NTHREADS) attn_decode_kernel(AttnArgs a, int c
 }
 
 // out[tok, h, :] = sum_s w_s * O_s / sum_s w_s,  w_s = 2^(lse_s - max lse).
+// One warp per (token, head): the lanes first share the splits (maximum and sum of the weights by
+// shuffles), then each lane owns four output columns per 128 and reads the partial outputs with
+// 16-byte loads when the workspace is 16-byte aligned and D a multiple of 4 (else the scalar loop).
+constexpr int kCombineWarps = 8;
 template <typename T>
-__global__ void __launch_bounds__(128) attn_combine_kernel(AttnArgs a) {
-  const int64_t tok = blockIdx.x;
-  const int h = blockIdx.y;
+__global__ void __launch_bounds__(kCombineWarps * 32) attn_combine_kernel(AttnArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t pair = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);   // (token, head), head fastest
+  if (pair >= a.total_q * a.H) return;
+  const int64_t tok = pair / a.H;
+  const int h = (int)(pair - tok * a.H);
+  const float* lse = a.ws_lse + (int64_t)h * a.total_q + tok;   // split s at lse[s * H * total_q]
+  const int64_t lse_step = (int64_t)a.H * a.total_q;
   float m = -INFINITY;
-  for (int s = 0; s < a.num_splits; ++s)
-    m = fmaxf(m, a.ws_lse[((int64_t)s * a.H + h) * a.total_q + tok]);
+  for (int s = lane; s < a.num_splits; s += 32) m = fmaxf(m, lse[s * lse_step]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
   const float msafe = m == -INFINITY ? 0.f : m;
   float wsum = 0.f;
-  for (int s = 0; s < a.num_splits; ++s)
-    wsum += exp2f(a.ws_lse[((int64_t)s * a.H + h) * a.total_q + tok] - msafe);
+  for (int s = lane; s < a.num_splits; s += 32) wsum += exp2f(lse[s * lse_step] - msafe);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, o);
   const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
-  for (int d = threadIdx.x; d < a.D; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s = 0; s < a.num_splits; ++s) {
-      const float w = exp2f(a.ws_lse[((int64_t)s * a.H + h) * a.total_q + tok] - msafe);
-      if (w > 0.f) acc += w * a.ws_o[(((int64_t)s * a.total_q + tok) * a.H + h) * a.D + d];
+  const float* part = a.ws_o + (tok * a.H + h) * (int64_t)a.D;   // split s at part[s * total_q * H * D]
+  const int64_t part_step = a.total_q * (int64_t)a.H * a.D;
+  T* out = reinterpret_cast<T*>(a.out) + tok * a.o_rs + (int64_t)h * a.o_hs;
+  if ((a.D & 3) == 0 && (reinterpret_cast<uintptr_t>(a.ws_o) & 15) == 0) {
+    for (int d = lane * 4; d < a.D; d += 128) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < a.num_splits; ++s) {
+        const float w = exp2f(lse[s * lse_step] - msafe);
+        if (w > 0.f) {
+          const float4 v = *reinterpret_cast<const float4*>(part + s * part_step + d);
+          acc.x += w * v.x;
+          acc.y += w * v.y;
+          acc.z += w * v.z;
+          acc.w += w * v.w;
+        }
+      }
+      out[d] = Cvt<T>::from_f32(acc.x * inv);
+      out[d + 1] = Cvt<T>::from_f32(acc.y * inv);
+      out[d + 2] = Cvt<T>::from_f32(acc.z * inv);
+      out[d + 3] = Cvt<T>::from_f32(acc.w * inv);
     }
-    reinterpret_cast<T*>(a.out)[tok * a.o_rs + (int64_t)h * a.o_hs + d] = Cvt<T>::from_f32(acc * inv);
+  } else {
+    for (int d = lane; d < a.D; d += 32) {
+      float acc = 0.f;
+      for (int s = 0; s < a.num_splits; ++s) {
+        const float w = exp2f(lse[s * lse_step] - msafe);
+        if (w > 0.f) acc += w * part[s * part_step + d];
+      }
+      out[d] = Cvt<T>::from_f32(acc * inv);
+    }
   }
-  if (a.lse && threadIdx.x == 0)
+  if (a.lse && lane == 0)
     a.lse[(int64_t)h * a.total_q + tok] = wsum > 0.f ? (m + log2f(wsum)) * 0.6931471805599453f : INFINITY;
+}
+
+static inline unsigned combine_grid(const AttnArgs& a) {
+  return (unsigned)((a.total_q * (int64_t)a.H + kCombineWarps - 1) / kCombineWarps);
 }
 
 template <typename T, int DP, int STAGES>
@@ -291,8 +329,7 @@ int launch_decode(const AttnArgs& a, int chunk_tokens, cudaStream_t st) {
   attn_decode_kernel<T, DP, STAGES><<<grid, NTHREADS, smem, st>>>(a, chunk_tokens);
   FG_CHECK_LAUNCH("attn_decode_kernel");
   if (a.num_splits > 1) {
-    dim3 cgrid((unsigned)a.total_q, a.H);
-    attn_combine_kernel<T><<<cgrid, 128, 0, st>>>(a);
+    attn_combine_kernel<T><<<combine_grid(a), kCombineWarps * 32, 0, st>>>(a);
     FG_CHECK_LAUNCH("attn_combine_kernel");
   }
   return FG_OK;
@@ -331,11 +368,10 @@ int attn_decode_tma(const AttnArgs& a, int dtype, int chunk_tokens, cudaStream_t
 
 // Combine pass shared by both decode kernels.
 int launch_decode_combine(const AttnArgs& a, int dtype, cudaStream_t st) {
-  dim3 cgrid((unsigned)a.total_q, a.H);
   if (dtype == FG_BF16)
-    attn_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, st>>>(a);
+    attn_combine_kernel<__nv_bfloat16><<<combine_grid(a), kCombineWarps * 32, 0, st>>>(a);
   else
-    attn_combine_kernel<__half><<<cgrid, 128, 0, st>>>(a);
+    attn_combine_kernel<__half><<<combine_grid(a), kCombineWarps * 32, 0, st>>>(a);
   FG_CHECK_LAUNCH("attn_combine_kernel");
   return FG_OK;
 }
