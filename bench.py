@@ -229,7 +229,8 @@ class Step:
         # The projections come first: with N > 1 their output shards are all-gathered on a side
         # stream while the rest of the step runs.  There a small projection leads so that NVLink is
         # already busy while the largest one (gate_up) computes; gate_up follows at once because
-        # its gather is the longest transfer of the step.  (On one GPU the order is immaterial.)
+        # its gather is the longest transfer of the step.  (On one GPU the projections are tensor-bound and their
+        # order among themselves is immaterial.)
         for name in (("qkv", "gate_up", "down", "o") if self.world > 1 else ("gate_up", "qkv", "down", "o")):
             a, b, bias, c, gathered = self.gemm[name]
             M, K = a.shape
