@@ -104,8 +104,26 @@ struct PrefillArgs {
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  // volatile: the exponentials of a step stay in program order, back to back
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// Packed pairs of fp32 (two lanes of one 64-bit register): (a0, a1) = (a0, a1) * sc + ng and
+// (s0, s1) += (p0, p1) as single instructions.
+__device__ __forceinline__ uint64_t pack2f(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void fma2(float& a0, float& a1, uint64_t sc, uint64_t ng) {
+  asm("{\n .reg .b64 x, r;\n mov.b64 x, {%0, %1};\n fma.rn.f32x2 r, x, %2, %3;\n mov.b64 {%0, %1}, r;\n}\n"
+      : "+f"(a0), "+f"(a1)
+      : "l"(sc), "l"(ng));
+}
+__device__ __forceinline__ void add2(float& s0, float& s1, float p0, float p1) {
+  asm("{\n .reg .b64 x, y, r;\n mov.b64 x, {%0, %1};\n mov.b64 y, {%2, %3};\n add.rn.f32x2 r, x, y;\n mov.b64 {%0, %1}, r;\n}\n"
+      : "+f"(s0), "+f"(s1)
+      : "f"(p0), "f"(p1));
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
@@ -520,14 +538,25 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         // ---- probabilities -> 32 packed 32-bit columns over the start of the score buffer
         // (the scores are all in registers, so P may overwrite them in TMEM)
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        // Three passes over the 64 scores in registers -- exponent arguments, exponentials, then sums and
+        // packing -- with the exponentials kept in program order (volatile): 64 independent
+        // special-function instructions back to back instead of short fma -> ex2 -> add chains.  The
+        // arguments and the row sums use the packed fp32 pair instructions (fma/add .f32x2): 2.5
+        // instead of 3.5 instructions per score (+3 % on the whole kernel, measured).
+        {
+          const uint64_t sc2 = pack2f(scale, scale), ng2 = pack2f(neg_m, neg_m);
+#pragma unroll
+          for (int e = 0; e < 64; e += 2) fma2(sv[e], sv[e + 1], sc2, ng2);
+        }
+#pragma unroll
+        for (int e = 0; e < 64; ++e) sv[e] = ex2(sv[e]);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           uint32_t pk[16];
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
-            const float p0 = ex2(fmaf(sv[q * 32 + 2 * e], scale, neg_m));
-            const float p1 = ex2(fmaf(sv[q * 32 + 2 * e + 1], scale, neg_m));
-            sum4[e & 3] += p0 + p1;
+            const float p0 = sv[q * 32 + 2 * e], p1 = sv[q * 32 + 2 * e + 1];
+            add2(sum4[(e & 1) * 2], sum4[(e & 1) * 2 + 1], p0, p1);
             pk[e] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
           }
           tmem_st16(sb_addr + q * 16, pk);
