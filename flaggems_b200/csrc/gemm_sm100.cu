@@ -12,7 +12,8 @@
 //               128-byte-swizzled shared-memory ring
 //   warp 1      allocates TMEM and issues tcgen05.mma (M128 N256 K16) from one thread
 //   warps 2-9   epilogue (two warps per TMEM lane quarter, 128 columns each): tcgen05.ld the
-//               accumulator, alpha/beta/bias in fp32, round once, 16-byte stores
+//               accumulator, alpha/beta/bias in fp32, round once, transpose 32 rows x 64 columns
+//               through a per-warp shared-memory tile and store whole 128-byte row segments
 // Both operands may be row- or column-major; the UMMA descriptors carry the
 // majorness, the TMA boxes differ (one [64 x rows] box for a K-major operand, one
 // [64 x 64] box per 64 rows for an MN-major operand).  M, N and K tails are handled
@@ -38,7 +39,8 @@ struct Cfg {
   static constexpr int A_STAGE_BYTES = TILE_M * BK * 2;  // 16 / 32 KB
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 };
-constexpr int SMEM_BYTES = 4 * (BM * BK * 2 + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/;  // both shapes: 192 KB
+constexpr int EPI_STAGE_BYTES = 32 * 128;   // per epilogue warp: 32 rows x 64 output columns of 16 bits
+constexpr int SMEM_BYTES = 4 * (BM * BK * 2 + B_STAGE_BYTES) + 1024 /*align*/ + 256 /*barriers*/ + 8 * EPI_STAGE_BYTES;  // ring 192 KB + 32 KB
 constexpr int NUM_THREADS = 320;   // TMA warp, MMA warp, 8 epilogue warps
 constexpr int TMEM_COLS = 512;
 
@@ -269,58 +271,102 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       tc_fence_after();
       const int64_t col0 = tn * BN;
       const T* bias = reinterpret_cast<const T*>(g.bias) + bi * g.bias_bs;
-#pragma unroll 1
-      for (int mt = 0; mt < nh; ++mt) {
-      const int64_t row = tm * TILE_M + (h0 + mt) * BM + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf + mt) * BN);
-      T* crow = reinterpret_cast<T*>(g.c) + bi * g.c_bs + row * g.c_s0;
-#pragma unroll 1
-      for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        const int64_t col = col0 + c * 32;
-        if (row < g.M && col < g.N) {
-          float v[32];
+      // alpha * acc (+ beta * bias) of one 32-column chunk of this lane's row
+      auto scale_chunk = [&](const uint32_t (&r)[32], int64_t row, int64_t col, float (&v)[32]) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          if (g.has_bias) {
-            if (g.bias_vec && col + 32 <= g.N) {
-              // the usual addmm bias, a row vector: four 16-byte loads (the same addresses in
-              // every lane) instead of 32 strided scalar ones
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                float bv[8];
-                Vec16<T>::unpack(ldg16(bias + col + q * 8), bv);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[q * 8 + j] = fmaf(v[q * 8 + j], g.alpha, bv[j] * g.beta);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int64_t cj = col + j;
-                const float bv = cj < g.N ? Cvt<T>::to_f32(bias[row * g.bias_s0 + cj * g.bias_s1]) : 0.f;
-                v[j] = v[j] * g.alpha + bv * g.beta;
-              }
-            }
-          }
-          if (g.c_vec_ok && col + 32 <= g.N) {
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (g.has_bias) {
+          if (g.bias_vec && col + 32 <= g.N) {
+            // the usual addmm bias, a row vector: four 16-byte loads (the same addresses in
+            // every lane) instead of 32 strided scalar ones
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              uint4 o;
-              o.x = pack2<T>(v[q * 8 + 0], v[q * 8 + 1]);
-              o.y = pack2<T>(v[q * 8 + 2], v[q * 8 + 3]);
-              o.z = pack2<T>(v[q * 8 + 4], v[q * 8 + 5]);
-              o.w = pack2<T>(v[q * 8 + 6], v[q * 8 + 7]);
-              *reinterpret_cast<uint4*>(crow + col + q * 8) = o;
+              float bv[8];
+              Vec16<T>::unpack(ldg16(bias + col + q * 8), bv);
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[q * 8 + j] = fmaf(v[q * 8 + j], g.alpha, bv[j] * g.beta);
             }
           } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col + j < g.N) crow[col + j] = Cvt<T>::from_f32(v[j]);
+            for (int j = 0; j < 32; ++j) {
+              const int64_t cj = col + j;
+              const float bv = (cj < g.N && row < g.M) ? Cvt<T>::to_f32(bias[row * g.bias_s0 + cj * g.bias_s1]) : 0.f;
+              v[j] = v[j] * g.alpha + bv * g.beta;
+            }
           }
         }
-      }
+      };
+      // Whole 64-column groups inside N with 16-byte stores allowed go through a per-warp staging
+      // tile in shared memory: a lane converts its own row (TMEM lane = row), the warp then writes
+      // four rows x 128 contiguous bytes per store instruction instead of 32 rows x 16 bytes.
+      const bool staged = g.c_vec_ok && col0 + BN <= g.N;
+      uint8_t* stage = bars_base + 256 + (warp - 2) * EPI_STAGE_BYTES;
+#pragma unroll 1
+      for (int mt = 0; mt < nh; ++mt) {
+        const int64_t row0 = tm * TILE_M + (h0 + mt) * BM + quarter * 32;
+        const int64_t row = row0 + lane;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf + mt) * BN);
+        T* cbase = reinterpret_cast<T*>(g.c) + bi * g.c_bs;
+        if (staged) {
+#pragma unroll 1
+          for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); c += 2) {
+            const int64_t col = col0 + c * 32;
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+              uint32_t r[32];
+              tmem_ld32(taddr + (c + hc) * 32, r);
+              tmem_ld_wait();
+              float v[32];
+              scale_chunk(r, row, col + hc * 32, v);
+              // 16-byte packet j of the row goes to slot j ^ (row & 7): conflict-free both ways
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                uint4 o;
+                o.x = pack2<T>(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack2<T>(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack2<T>(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack2<T>(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(stage + lane * 128 + (((hc * 4 + q) ^ (lane & 7)) << 4)) = o;
+              }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3), j = lane & 7;
+              const uint4 o = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((j ^ (rr & 7)) << 4));
+              if (row0 + rr < g.M) *reinterpret_cast<uint4*>(cbase + (row0 + rr) * g.c_s0 + col + j * 8) = o;
+            }
+            __syncwarp();
+          }
+        } else {
+          T* crow = cbase + row * g.c_s0;
+#pragma unroll 1
+          for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+            const int64_t col = col0 + c * 32;
+            if (row < g.M && col < g.N) {
+              float v[32];
+              scale_chunk(r, row, col, v);
+              if (g.c_vec_ok && col + 32 <= g.N) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  uint4 o;
+                  o.x = pack2<T>(v[q * 8 + 0], v[q * 8 + 1]);
+                  o.y = pack2<T>(v[q * 8 + 2], v[q * 8 + 3]);
+                  o.z = pack2<T>(v[q * 8 + 4], v[q * 8 + 5]);
+                  o.w = pack2<T>(v[q * 8 + 6], v[q * 8 + 7]);
+                  *reinterpret_cast<uint4*>(crow + col + q * 8) = o;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col + j < g.N) crow[col + j] = Cvt<T>::from_f32(v[j]);
+              }
+            }
+          }
+        }
       }
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);
