@@ -73,6 +73,11 @@ class AttnParams(C.Structure):
     )
 
 
+class GemmPlan(C.Structure):
+    _fields_ = ([(n, C.c_int32) for n in ("tile_m", "tile_n", "grid", "group_m")]
+                + [(n, C.c_int64) for n in ("tiles_m", "tiles_n", "full_units", "num_units")])
+
+
 class SchedulerParams(C.Structure):
     _fields_ = (
         [(n, C.c_int32) for n in (
@@ -112,6 +117,7 @@ SIGNATURES = {
     "fg_gemm": (C.c_int, [C.POINTER(GemmParams), _P]),
     "fg_gemm_batched": (C.c_int, [C.POINTER(GemmParams)] + [_I64] * 5 + [_P]),
     "fg_gemm_uses_tcgen05": (C.c_int, [C.POINTER(GemmParams)]),
+    "fg_gemm_tile_plan": (C.c_int, [C.POINTER(GemmParams), _I64, C.c_int, C.POINTER(GemmPlan)]),
     "fg_flash_attn_varlen": (C.c_int, [C.POINTER(AttnParams), _P]),
     "fg_flash_attn_workspace_bytes": (C.c_int64, [_I64] * 5),
     "fg_flash_attn_path": (C.c_int, [C.POINTER(AttnParams)]),

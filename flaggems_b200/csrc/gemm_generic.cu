@@ -87,6 +87,13 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GArgs g) {
 }  // namespace
 }  // namespace fg
 
+namespace fg {
+int gemm_tile_plan(const fg_gemm_params* p, int64_t batch, int num_sms, fg_gemm_plan* out);
+}
+extern "C" int fg_gemm_tile_plan(const fg_gemm_params* p, int64_t batch, int num_sms, fg_gemm_plan* out) {
+  return fg::gemm_tile_plan(p, batch, num_sms, out);
+}
+
 extern "C" int fg_gemm_uses_tcgen05(const fg_gemm_params* p) {
   return (p != nullptr && fg::gemm_tcgen05_eligible(p)) ? 1 : 0;
 }

@@ -428,6 +428,57 @@ static bool tcgen05_eligible(const fg_gemm_params* p) {
   return true;
 }
 
+// Tile shape and work units of a launch: pure host arithmetic, also served by fg_gemm_tile_plan.
+struct TilePlan {
+  int mt;              // 1: 128x256 tiles, 2: 256x256 tiles
+  int sms, grid, group_m;
+  int64_t tiles_m, tiles_n, tiles;   // row tiles (of mt * 128 rows), column tiles, tiles over the batch
+  int64_t full_units, num_units;     // units [0, full_units) are whole tiles, the rest 128-row halves
+};
+
+static TilePlan plan_tiles(const fg_gemm_params* p, int64_t batch, int sms, bool a_mn) {
+  // Tile shape: 256x256 needs a third less operand traffic per flop but has half as many,
+  // twice as long tiles; it is taken when its last, partly filled wave costs less than that
+  // gains, for K-major A only.  Measured at M = 8192 (bf16, B200): 1461 against 1392 TFLOP/s
+  // for N = 28672, K = 4096 with bias, 1504 against 1356 for N = 4096, K = 14336, a tie for
+  // N = 6144 where the big tile's sixth wave is a fifth full.
+  TilePlan t;
+  t.sms = sms;
+  const int64_t tn = (p->N + BN - 1) / BN;
+  const int64_t tiles1 = ((p->M + BM - 1) / BM) * tn * batch;
+  const int64_t tiles2 = ((p->M + 2 * BM - 1) / (2 * BM)) * tn * batch;
+  const int64_t waves1 = (tiles1 + sms - 1) / sms;
+  // A last wave of 256x256 tiles that fills at most half of the SMs is cut into 128-row halves,
+  // one per CTA: it then takes about 0.56 of a tile time (one MMA per K step, B no longer shared).
+  const int64_t rest2 = tiles2 % sms;
+  const bool split_tail = g_split_tail && tiles2 > sms && rest2 > 0 && 2 * rest2 <= sms;
+  const double waves2 = (double)(tiles2 / sms) + (rest2 == 0 ? 0.0 : split_tail ? kHalfTileCost : 1.0);
+  t.mt = (!a_mn && p->M > BM && waves2 * 2.0 * kBigTileCost < (double)waves1) ? 2 : 1;
+  if (g_force_mt == 1 || (g_force_mt == 2 && !a_mn)) t.mt = g_force_mt;
+  const int tile_m = t.mt * BM;
+  t.tiles_m = (p->M + tile_m - 1) / tile_m;
+  t.tiles_n = tn;
+  t.tiles = t.mt == 2 ? tiles2 : tiles1;
+  t.grid = t.tiles < sms ? (int)t.tiles : sms;
+  t.full_units = (t.mt == 2 && split_tail) ? t.tiles - rest2 : t.tiles;
+  t.num_units = t.full_units + 2 * (t.tiles - t.full_units);
+  // Row tiles per sweep over the column tiles: as many as keep the A panel of a group
+  // (group_m x tile rows x K) around 32 MB, so that it stays L2-resident while B streams
+  // through once per group instead of once per few row tiles.
+  const int64_t panel = (int64_t)tile_m * p->K * 2;
+  int64_t gm = (32ll << 20) / (panel > 0 ? panel : 1);
+  if (gm < 4) gm = 4;
+  if (gm > 64) gm = 64;
+  t.group_m = (int)gm;
+  return t;
+}
+
+static bool a_is_mn_major(const fg_gemm_params* p) {
+  // A: K-major if a_stride1 == 1 (row-major), else M-major.  Degenerate shapes with
+  // both strides 1 are treated as row-major.
+  return !(p->a_stride1 == 1 && p->a_stride0 % 8 == 0 && p->a_stride0 >= p->K);
+}
+
 template <typename T, int MT>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& ta_half, const CUtensorMap& tb, const GemmArgs& g,
                        int grid, cudaStream_t st) {
@@ -446,30 +497,12 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& ta_half, const 
 
 int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) {
   using namespace fg;
-  // A: K-major if a_stride1 == 1 (row-major), else M-major.  Degenerate shapes with
-  // both strides 1 are treated as row-major.
-  const bool a_mn = !(p->a_stride1 == 1 && p->a_stride0 % 8 == 0 && p->a_stride0 >= p->K);
+  const bool a_mn = a_is_mn_major(p);
   // B [K,N]: K-major if b_stride0 == 1 (column-major storage), else N-major.
   const bool b_mn = !(p->b_stride0 == 1 && p->b_stride1 % 8 == 0 && p->b_stride1 >= p->K);
 
-  // Tile shape: 256x256 needs a third less operand traffic per flop but has half as many,
-  // twice as long tiles; it is taken when its last, partly filled wave costs less than that
-  // gains, for K-major A only.  Measured at M = 8192 (bf16, B200): 1461 against 1392 TFLOP/s
-  // for N = 28672, K = 4096 with bias, 1504 against 1356 for N = 4096, K = 14336, a tie for
-  // N = 6144 where the big tile's sixth wave is a fifth full.
-  const int sms = sm_budget();
-  const int64_t tn = (p->N + BN - 1) / BN;
-  const int64_t tiles1 = ((p->M + BM - 1) / BM) * tn * bt.batch;
-  const int64_t tiles2 = ((p->M + 2 * BM - 1) / (2 * BM)) * tn * bt.batch;
-  const int64_t waves1 = (tiles1 + sms - 1) / sms;
-  // A last wave of 256x256 tiles that fills at most half of the SMs is cut into 128-row halves,
-  // one per CTA: it then takes about 0.56 of a tile time (one MMA per K step, B no longer shared).
-  const int64_t rest2 = tiles2 % sms;
-  const bool split_tail = g_split_tail && tiles2 > sms && rest2 > 0 && 2 * rest2 <= sms;
-  const double waves2 = (double)(tiles2 / sms) + (rest2 == 0 ? 0.0 : split_tail ? kHalfTileCost : 1.0);
-  int mt = (!a_mn && p->M > BM && waves2 * 2.0 * kBigTileCost < (double)waves1) ? 2 : 1;
-  if (g_force_mt == 1 || (g_force_mt == 2 && !a_mn)) mt = g_force_mt;
-  const int tile_m = mt * BM;
+  const TilePlan plan = plan_tiles(p, bt.batch, sm_budget(), a_mn);
+  const int sms = plan.sms, mt = plan.mt, tile_m = mt * BM;
 
   CUtensorMap ta, ta_half, tb;
   {
@@ -514,16 +547,7 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
   g.has_bias = p->bias != nullptr;
   g.a_mn_major = a_mn; g.b_mn_major = b_mn;
   g.is_bf16 = p->dtype == FG_BF16;
-  // Row tiles per sweep over the column tiles: as many as keep the A panel of a group
-  // (group_m x tile rows x K) around 32 MB, so that it stays L2-resident while B streams
-  // through once per group instead of once per few row tiles.
-  {
-    const int64_t panel = (int64_t)tile_m * p->K * 2;
-    int64_t gm = (32ll << 20) / (panel > 0 ? panel : 1);
-    if (gm < 4) gm = 4;
-    if (gm > 64) gm = 64;
-    g.group_m = (int)gm;
-  }
+  g.group_m = plan.group_m;
   g.c_vec_ok = aligned16(p->c) && (p->c_stride0 % 8 == 0) && (bt.batch == 1 || bt.c_bs % 8 == 0);
   g.bias_vec = p->bias != nullptr && p->bias_stride0 == 0 && p->bias_stride1 == 1 && aligned16(p->bias) &&
                (bt.batch == 1 || bt.bias_bs % 8 == 0);
@@ -531,11 +555,10 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
   g.status = device_status_ptr();
   if (!g.status) return fail(FG_ERR_CUDA, "gemm: device status word unavailable");
 
-  const int64_t tiles = mt == 2 ? tiles2 : tiles1;
-  int grid = sms;  // persistent: one CTA per SM it may use
-  if (tiles < grid) grid = (int)tiles;
-  g.full_units = (mt == 2 && split_tail) ? tiles - rest2 : tiles;
-  g.num_units = g.full_units + 2 * (tiles - g.full_units);
+  const int grid = plan.grid;   // persistent: one CTA per SM it may use
+  g.full_units = plan.full_units;
+  g.num_units = plan.num_units;
+  (void)sms;
   if (p->dtype == FG_BF16)
     return mt == 2 ? launch_gemm<__nv_bfloat16, 2>(ta, ta_half, tb, g, grid, st)
                    : launch_gemm<__nv_bfloat16, 1>(ta, ta_half, tb, g, grid, st);
@@ -543,5 +566,21 @@ int gemm_tcgen05(const fg_gemm_params* p, const GemmBatch& bt, cudaStream_t st) 
 }
 
 bool gemm_tcgen05_eligible(const fg_gemm_params* p) { return tcgen05_eligible(p); }
+
+int gemm_tile_plan(const fg_gemm_params* p, int64_t batch, int num_sms, fg_gemm_plan* out) {
+  if (!p || !out) return fail(FG_ERR_INVALID, "gemm_tile_plan: null pointer");
+  if (batch < 1 || num_sms < 1) return fail(FG_ERR_INVALID, "gemm_tile_plan: batch and num_sms must be positive");
+  if (!tcgen05_eligible(p)) return fail(FG_ERR_UNSUPPORTED, "gemm_tile_plan: the generic kernel takes this problem");
+  const TilePlan t = plan_tiles(p, batch, num_sms, a_is_mn_major(p));
+  out->tile_m = t.mt * BM;
+  out->tile_n = BN;
+  out->grid = t.grid;
+  out->group_m = t.group_m;
+  out->tiles_m = t.tiles_m;
+  out->tiles_n = t.tiles_n;
+  out->full_units = t.full_units;
+  out->num_units = t.num_units;
+  return FG_OK;
+}
 
 }  // namespace fg

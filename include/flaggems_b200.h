@@ -204,6 +204,18 @@ FG_API int fg_gemm_batched(const fg_gemm_params* p, int64_t batch, int64_t a_bat
  * generic path.  Pure host logic (no CUDA call). */
 FG_API int fg_gemm_uses_tcgen05(const fg_gemm_params* p);
 
+/* How the tcgen05 kernel would cut the problem up on `num_sms` SMs (pure host logic, no CUDA
+ * call; FG_ERR_UNSUPPORTED when the generic kernel takes the problem).  The output is
+ * tiles_m x tiles_n tiles of tile_m x tile_n per batch member; the persistent grid walks
+ * num_units work units round-robin: units [0, full_units) are whole tiles (unit = tile index,
+ * batch-major, then grouped: group_m row tiles share a sweep over the column tiles), each later
+ * pair of units is the upper and lower 128-row half of one of the remaining tiles. */
+typedef struct {
+  int32_t tile_m, tile_n, grid, group_m;
+  int64_t tiles_m, tiles_n, full_units, num_units;
+} fg_gemm_plan;
+FG_API int fg_gemm_tile_plan(const fg_gemm_params* p, int64_t batch, int num_sms, fg_gemm_plan* plan);
+
 /* ------------------------------------------------------------------------
  * flash_attn_varlen: FlashAttention-2 style forward over variable-length
  * sequences with a paged or contiguous KV store.

@@ -204,3 +204,64 @@ def test_scheduler_plan_matches_the_oracle_plan():
         fg.scheduler_plan(4, 1, 512, 8, 8, 128, 128, arch=80)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         fg.get_scheduler_metadata(2, 1, 512, 8, 8, 128, 128, torch.bfloat16, torch.tensor([5, 9], dtype=torch.int32))
+
+
+def test_gemm_tile_plan_covers_every_output_block_once():
+    """fg_gemm_tile_plan is the host half of the tensor-core GEMM launch: tile shape, persistent
+    grid and work units (whole tiles, then 128-row halves of the tiles of a last wave that fills at
+    most half of the SMs).  Walking the units the way the kernel does must touch every 128-row
+    block of every column tile of every batch member exactly once."""
+    lib = _lib.load()
+
+    def plan(M, N, K, batch=1, sms=148, **kw):
+        out = _lib.GemmPlan()
+        p = _gemm_params(M, N, K, **kw)
+        rc = lib.fg_gemm_tile_plan(ctypes.byref(p), batch, sms, ctypes.byref(out))
+        return rc, out
+
+    def walk(pl, M, batch):
+        seen = {}
+        tiles_per_batch = pl.tiles_m * pl.tiles_n
+        halves = pl.tile_m // 128
+        for cta in range(pl.grid):
+            for u in range(cta, pl.num_units, pl.grid):
+                if halves == 1 or u < pl.full_units:
+                    tile, h0, nh = u, 0, halves
+                else:
+                    r = u - pl.full_units
+                    tile, h0, nh = pl.full_units + r // 2, r % 2, 1
+                bi, t = divmod(tile, tiles_per_batch)
+                per_group = pl.group_m * pl.tiles_n          # grouped order of the kernel's tile_coords
+                g = t // per_group
+                first_m = g * pl.group_m
+                rows = min(pl.tiles_m - first_m, pl.group_m)
+                r = t - g * per_group
+                tm, tn = first_m + r % rows, r // rows
+                for h in range(h0, h0 + nh):
+                    key = (bi, tm * halves + h, tn)
+                    seen[key] = seen.get(key, 0) + 1
+        blocks_m = pl.tiles_m * halves
+        assert len(seen) == batch * blocks_m * pl.tiles_n and set(seen.values()) == {1}
+        assert blocks_m * 128 >= M
+
+    cases = [(8192, 28672, 4096, 1), (8192, 6144, 4096, 1), (8192, 4096, 14336, 1), (8192, 4096, 4096, 1),
+             (2100, 4608, 512, 1), (2048, 28672, 256, 1), (129, 264, 72, 1), (300, 16, 4096, 1), (1024, 1024, 1024, 32),
+             (1000, 520, 264, 7), (4096, 4096, 4096, 1), (8192, 4096, 512, 1)]
+    for M, N, K, batch in cases:
+        for sms in (148, 132, 20):
+            rc, pl = plan(M, N, K, batch, sms)
+            assert rc == 0, (M, N, K, batch, sms)
+            assert pl.tile_n == 256 and pl.tile_m in (128, 256) and 1 <= pl.grid <= sms
+            assert pl.tiles_m == -(-M // pl.tile_m) and pl.tiles_n == -(-N // 256)
+            assert pl.full_units <= pl.num_units and (pl.num_units - pl.full_units) % 2 == 0
+            # halves only for 256-row tiles, at most one per CTA, after whole waves
+            if pl.num_units > pl.full_units:
+                assert pl.tile_m == 256 and pl.full_units % pl.grid == 0 and pl.num_units - pl.full_units <= pl.grid
+            walk(pl, M, batch)
+    # the benchmark projections take the big tile; the last wave of o / down (68 tiles) is halved
+    rc, pl = plan(8192, 4096, 4096)
+    assert (pl.tile_m, pl.full_units, pl.num_units) == (256, 444, 444 + 136)
+    # column-major A keeps the 128-row tile; the generic kernel's problems have no plan
+    rc, pl = plan(8192, 6144, 4096, a_strides=(1, 8192))
+    assert rc == 0 and pl.tile_m == 128
+    assert plan(495, 5333, 71)[0] == -2 and plan(8192, 6144, 4096, 0)[0] == -1
