@@ -11,6 +11,8 @@ therefore pinned against the reference's own test oracles *executed from the ref
 checkout*: ``tests/golden/make_golden.py`` extracts those oracle functions from the
 reference's test files, runs them on seeded inputs and stores inputs and outputs as
 fixtures; ``tests/test_oracle_golden.py`` replays the fixtures through this module.
+The two cache scatters are in addition accepted by the reference's own test functions, executed
+with these functions standing in for the operators (``tests/golden/make_golden_cache_tests.py``).
 ``get_scheduler_metadata`` is pinned against results of the reference function itself
 (``tests/golden/make_golden_scheduler.py`` runs it under Triton's interpreter).
 

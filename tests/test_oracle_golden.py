@@ -102,3 +102,17 @@ def test_scheduler_metadata_matches_reference_run(golden_dir):
     for i, c in enumerate(cases):
         got = O.get_scheduler_metadata(sm_count=c["sm_count"], **_scheduler_kwargs(c))
         assert got.dtype == torch.int32 and torch.equal(got, c["metadata"]), i
+
+
+def test_cache_oracles_replay_what_the_reference_tests_accepted(golden_dir):
+    """``golden_cache_tests.pt``: inputs drawn by the reference's own ``test_reshape_and_cache`` and
+    ``test_reshape_and_cache_flash`` and the caches those tests accepted (the tests ran from the
+    reference checkout with the oracle standing in for the operator)."""
+    cases = _load(golden_dir, "golden_cache_tests.pt")
+    assert {c["layout"] for c in cases} == {"v0", "flash"} and len(cases) >= 7
+    for c in cases:
+        kc, vc = c["key_cache"].clone(), c["value_cache"].clone()
+        fn = O.reshape_and_cache if c["layout"] == "v0" else O.reshape_and_cache_flash
+        fn(c["key"], c["value"], kc, vc, c["slot_mapping"])
+        assert torch.equal(kc, c["key_cache_out"]) and torch.equal(vc, c["value_cache_out"])
+        assert not torch.equal(kc, c["key_cache"])
