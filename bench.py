@@ -594,45 +594,48 @@ def cpu_step_sample(seed=0):
         fn()
         return time.perf_counter() - t0
 
-    x, r, w, eps = W.norm_inputs(seed=seed + 1, T=1024, device="cpu")
-    t = timed(lambda: O.fused_add_rms_norm(x, r, w, eps, upcast=torch.float32)) * 4
+    x, r, w, eps = W.norm_inputs(seed=seed + 1, T=4096, device="cpu")
+    t = timed(lambda: O.fused_add_rms_norm(x, r, w, eps, upcast=torch.float32))
     detail["fused_add_rms_norm"] = t
-    q, k, cos, sin, pos = W.rope_inputs(seed=seed + 2, T=1024, device="cpu")
+    q, k, cos, sin, pos = W.rope_inputs(seed=seed + 2, T=4096, device="cpu")
     cos4, sin4 = W.rope_tables(4096, 128, torch.bfloat16, "cpu")
-    t = timed(lambda: O.apply_rotary_pos_emb(q, k, cos4, sin4, pos)) * 4
+    t = timed(lambda: O.apply_rotary_pos_emb(q, k, cos4, sin4, pos))
     detail["rotary_embedding"] = t
-    act = W.silu_inputs(seed=seed + 3, T=512, device="cpu")
+    act = W.silu_inputs(seed=seed + 3, T=2048, device="cpu")
     h = act.shape[1] // 2
-    t = timed(lambda: O.silu_and_mul(act[:, :h], act[:, h:], upcast=torch.float32)) * 8
+    t = timed(lambda: O.silu_and_mul(act[:, :h], act[:, h:], upcast=torch.float32)) * 2
     detail["silu_and_mul"] = t
-    # prefill: one 512-token sequence, scaled by FLOPs to the 16-sequence batch
+    # prefill: one 1024-token sequence, scaled by FLOPs to the 16-sequence batch
     g = torch.Generator().manual_seed(seed + 4)
     lens = torch.randint(128, 4097, (16,), generator=g).tolist()
-    pb = W.prefill_batch(seed=seed + 4, num_seqs=1, min_len=512, max_len=512, device="cpu")
+    pb = W.prefill_batch(seed=seed + 4, num_seqs=1, min_len=1024, max_len=1024, device="cpu")
     t1 = timed(lambda: O.paged_attention(pb.q, pb.key_cache, pb.value_cache, pb.query_lens, pb.kv_lens, pb.block_table,
                                          pb.scale, compute_dtype=torch.float32))
-    detail["flash_attn_varlen_func[prefill]"] = t1 * W.prefill_flops(lens) / W.prefill_flops([512])
-    # decode: 4 sequences with 2048-token contexts, scaled by context tokens
-    db = W.decode_batch(seed=seed + 5, batch=4, min_ctx=2048, max_ctx=2048, device="cpu")
+    detail["flash_attn_varlen_func[prefill]"] = t1 * W.prefill_flops(lens) / W.prefill_flops([1024])
+    # decode: 16 sequences with 2048-token contexts, scaled by context tokens
+    db = W.decode_batch(seed=seed + 5, batch=16, min_ctx=2048, max_ctx=2048, device="cpu")
     g = torch.Generator().manual_seed(seed + 5)
     ctx = torch.randint(512, 8193, (256,), generator=g).tolist()
     kc, vc = db.key_cache.clone(), db.value_cache.clone()
     t0 = timed(lambda: O.reshape_and_cache_flash(db.new_key, db.new_value, kc, vc, db.slot_mapping))
-    detail["reshape_and_cache_flash"] = t0 * 256 / 4
+    detail["reshape_and_cache_flash"] = t0 * 256 / 16
     t1 = timed(lambda: O.paged_attention(db.q, db.key_cache, db.value_cache, db.query_lens, db.kv_lens,
                                          db.block_table, db.scale, compute_dtype=torch.float32))
-    detail["flash_attn_varlen_func[decode]"] = t1 * sum(ctx) / (4 * 2048)
-    # projections: 128 of the 8192 rows
+    detail["flash_attn_varlen_func[decode]"] = t1 * sum(ctx) / (16 * 2048)
+    # projections: 512 of the 8192 rows
     for i, name in enumerate(W.GEMM_SHAPES):
-        a, b, bias = W.gemm_inputs(name, seed=seed + 10 + i, M=128, device="cpu")
+        a, b, bias = W.gemm_inputs(name, seed=seed + 10 + i, M=512, device="cpu")
+        # operands upcast beforehand, as the reference's harness does before it calls torch on the CPU
+        # (the weight's conversion does not grow with the rows and must not be scaled with them)
+        a, b, bias = a.float(), b.float(), bias.float()
         if name in ("qkv", "gate_up"):
             t = timed(lambda: O.addmm(bias, a, b, upcast=torch.float32))
         else:
             t = timed(lambda: O.mm(a, b, upcast=torch.float32))
-        detail[f"gemm[{name}]"] = t * 64
+        detail[f"gemm[{name}]"] = t * 16
     total = sum(detail.values())
-    sample = ("per operator: norm/rope 1024 of 4096 tokens, silu_and_mul 512 of 4096 rows, prefill one 512-token "
-              "sequence (scaled by FLOPs), decode 4 sequences x 2048 context (scaled by context tokens), GEMMs 128 "
+    sample = ("per operator: norm/rope all 4096 tokens, silu_and_mul 2048 of 4096 rows, prefill one 1024-token "
+              "sequence (scaled by FLOPs), decode 16 sequences x 2048 context (scaled by context tokens), GEMMs 512 "
               "of 8192 rows; fp32 torch CPU")
     return total, len(detail), sample, detail
 
@@ -641,7 +644,7 @@ def run_reference_arm(args, rank):
     if rank != 0:
         return
     cores = torch.get_num_threads()
-    for _ in range(min(args.warmup, 1)):
+    for _ in range(max(1, min(args.warmup, 1))):   # one untimed pass: page faults, thread pool start-up
         cpu_step_sample()
     times = []
     n_ops = 10
@@ -846,9 +849,10 @@ def main():
     if rank == 0 and world == 1 and args.triton_ref:
         out["triton_ref"] = triton_reference_times(step)
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_step_sample()   # untimed: first-touch page faults and the thread pool's start-up
         t, n, sample, detail = cpu_step_sample()
         out["cpu_baseline"] = {"value": n / t, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": sample, "step_seconds_scaled": t}
+                               "sample": sample + "; second of two passes", "step_seconds_scaled": t}
     if world > 1:
         # the same K steps without the all-gathers: what the sharded operators alone scale like
         step.skip_gather = True
