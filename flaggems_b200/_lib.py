@@ -14,7 +14,7 @@ from pathlib import Path
 import torch
 
 FG_F32, FG_F16, FG_BF16 = 0, 1, 2
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _DTYPE_CODE = {torch.float32: FG_F32, torch.float16: FG_F16, torch.bfloat16: FG_BF16}
 
@@ -105,6 +105,10 @@ SIGNATURES = {
     "fg_last_error": (C.c_char_p, []),
     "fg_launch_count": (C.c_int64, []),
     "fg_device_status": (C.c_int, [C.c_int]),
+    "fg_device_status_nosync": (C.c_int, []),
+    "fg_debug_set_status": (C.c_int, [C.c_int]),
+    "fg_debug_wait_timeout": (C.c_int, [C.c_int64, C.c_void_p, C.c_void_p]),
+    "fg_copy_2d": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
     "fg_set_num_sms": (C.c_int, [C.c_int]),
     "fg_get_num_sms": (C.c_int, []),
     "fg_fused_add_rms_norm": (C.c_int, [_P, _P, _P, _I64, _I64, _I64, _I64, C.c_double, C.c_int, _P]),
@@ -208,3 +212,10 @@ def device_status(reset: bool = False) -> int:
     rc = load().fg_device_status(1 if reset else 0)
     check(rc)
     return rc
+
+
+def device_status_nosync() -> int:
+    """The host-visible copy of the status word (no synchronisation).  Every launching entry
+    point of the library checks it itself and fails with FG_ERR_DEVICE while it is set, which
+    the wrappers of this package raise as RuntimeError."""
+    return int(load().fg_device_status_nosync())

@@ -48,6 +48,7 @@ extern "C" int64_t fg_flash_attn_workspace_bytes(int64_t batch, int64_t num_head
 
 extern "C" int fg_flash_attn_varlen(const fg_attn_params* p, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("flash_attn_varlen");
   FG_REQUIRE(p != nullptr, "flash_attn_varlen: null params");
   FG_REQUIRE(p->dtype == FG_F16 || p->dtype == FG_BF16, "FlashAttention only support fp16 and bf16 data type");
   FG_REQUIRE(p->batch >= 0 && p->total_q >= 0, "flash_attn_varlen: negative size");

@@ -53,6 +53,7 @@ extern "C" int64_t fg_flash_attn_decode_static_capacity(void) { return FG_DECODE
 
 extern "C" int fg_flash_attn_decode_static(const fg_attn_params* p, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("flash_attn_decode_static");
   FG_REQUIRE(p != nullptr, "flash_attn_decode_static: null params");
   FG_REQUIRE(p->max_seqlen_q == 1 && p->total_q == p->batch,
              "flash_attn_decode_static: exactly one query token per sequence is required");
@@ -73,6 +74,10 @@ extern "C" int fg_flash_attn_decode_static(const fg_attn_params* p, void* stream
   void* scratch = nullptr;
   const int rc = scratch_address(&scratch);
   if (rc != FG_OK) return rc;
+  // This entry point makes no allocating or page-locking call: if no other entry point has
+  // set up the host-visible copy of the device status word on this device yet, this call runs
+  // without it (a wait that gave up is then reported by fg_device_status only).
+  MirrorSetupGuard no_setup;
   fg_attn_params q = *p;
   q.workspace = scratch;
   q.workspace_bytes = FG_DECODE_STATIC_SCRATCH_BYTES;

@@ -31,6 +31,25 @@ inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_
       return ::fg::fail(FG_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
   } while (0)
 
+// Host-visible copy of the device status word (core.cu): non-zero after a kernel of this
+// library gave up a bounded wait on the current device.  Reading it costs a load from pinned
+// host memory, no synchronisation; every launching entry point refuses to launch while it is set.
+int drained_code();
+int fail_drained(const char* what, int code);
+#define FG_REQUIRE_HEALTHY(what)                              \
+  do {                                                        \
+    const int _dc = ::fg::drained_code();                     \
+    if (_dc != 0) return ::fg::fail_drained(what, _dc);       \
+  } while (0)
+// While one of these lives on a thread, device_status_ptr() does not perform the one-time
+// set-up of the host-visible copy (a cudaHostRegister): for entry points that promise to make
+// no allocating or registering call.
+struct MirrorSetupGuard {
+  MirrorSetupGuard();
+  ~MirrorSetupGuard();
+  bool saved_;
+};
+
 // Check the launch that was just issued (configuration errors only; no sync).
 #define FG_CHECK_LAUNCH(name)                                                        \
   do {                                                                               \

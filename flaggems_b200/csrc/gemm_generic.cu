@@ -128,6 +128,7 @@ static int gemm_checked(const char* what, const fg_gemm_params* p) {
 
 extern "C" int fg_gemm(const fg_gemm_params* p, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("gemm");
   const int rc = gemm_checked("gemm", p);
   if (rc != FG_OK) return rc < 0 ? rc : FG_OK;
   cudaStream_t st = (cudaStream_t)stream;
@@ -139,6 +140,7 @@ extern "C" int fg_gemm_batched(const fg_gemm_params* p, int64_t batch, int64_t a
                                int64_t b_batch_stride, int64_t c_batch_stride, int64_t bias_batch_stride,
                                void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("gemm_batched");
   const int rc = gemm_checked("gemm_batched", p);
   if (rc != FG_OK) return rc < 0 ? rc : FG_OK;
   FG_REQUIRE(batch >= 0, "gemm_batched: negative batch");

@@ -101,6 +101,7 @@ extern "C" int fg_reshape_and_cache_flash(const void* key, const void* value, vo
                                           int64_t cache_row_stride, int64_t cache_head_stride,
                                           int elem_size, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("reshape_and_cache_flash");
   FG_REQUIRE(num_tokens >= 0 && num_heads >= 0 && head_size >= 0, "reshape_and_cache_flash: negative size");
   FG_REQUIRE(block_size > 0 && num_blocks >= 0, "reshape_and_cache_flash: block_size must be positive");
   FG_REQUIRE(elem_size == 1 || elem_size == 2 || elem_size == 4,
@@ -153,6 +154,7 @@ extern "C" int fg_reshape_and_cache(const void* key, const void* value, void* ke
                                     int64_t head_size, int64_t block_size, int64_t num_blocks, int64_t x,
                                     int64_t key_stride, int64_t value_stride, int elem_size, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("reshape_and_cache");
   FG_REQUIRE(num_tokens >= 0 && num_heads >= 0 && head_size >= 0, "reshape_and_cache: negative size");
   FG_REQUIRE(block_size > 0 && num_blocks >= 0, "reshape_and_cache: block_size must be positive");
   FG_REQUIRE(x > 0 && head_size % x == 0, "reshape_and_cache: head_size %lld is not a multiple of x = %lld",

@@ -156,6 +156,7 @@ extern "C" int fg_fused_add_rms_norm(void* x, void* residual, const void* weight
                                      int64_t N, int64_t x_row_stride, int64_t r_row_stride,
                                      double eps, int dtype, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("fused_add_rms_norm");
   FG_REQUIRE(M >= 0 && N >= 0, "fused_add_rms_norm: negative size");
   if (M == 0 || N == 0) return FG_OK;
   FG_REQUIRE(x && residual && weight, "fused_add_rms_norm: null pointer");
@@ -171,6 +172,7 @@ extern "C" int fg_rms_norm(const void* x, const void* weight, void* out, int64_t
                            int64_t x_row_stride, int64_t o_row_stride, double eps, int dtype,
                            void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("rms_norm");
   FG_REQUIRE(M >= 0 && N >= 0, "rms_norm: negative size");
   if (M == 0 || N == 0) return FG_OK;
   FG_REQUIRE(x && out && weight, "rms_norm: null pointer");

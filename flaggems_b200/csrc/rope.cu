@@ -205,6 +205,7 @@ static int launch_rope(const fg_rope_params* p, cudaStream_t st) {
 
 extern "C" int fg_rotary_embedding(const fg_rope_params* p, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("rotary_embedding");
   FG_REQUIRE(p != nullptr, "rotary_embedding: null params");
   FG_REQUIRE(p->num_tokens >= 0 && p->q_heads >= 0 && p->k_heads >= 0, "rotary_embedding: negative size");
   FG_REQUIRE(p->head_dim > 0 && p->head_dim % 2 == 0, "rotary_embedding: head_dim %lld must be even and positive",

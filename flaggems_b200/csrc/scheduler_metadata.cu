@@ -227,6 +227,7 @@ extern "C" int fg_scheduler_plan(const FgSchedulerParams* p, FgSchedulerPlan* pl
 
 extern "C" int fg_get_scheduler_metadata(const FgSchedulerParams* p, int32_t* metadata, void* stream) {
   using namespace fg;
+  FG_REQUIRE_HEALTHY("get_scheduler_metadata");
   FgSchedulerPlan plan;
   const int rc = make_plan(p, &plan);
   if (rc != FG_OK) return rc;

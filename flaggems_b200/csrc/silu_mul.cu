@@ -174,6 +174,7 @@ namespace fg {
 static int act_and_mul(const char* what, int act, const void* a, const void* b, void* out, int ndim,
                        const int64_t* sizes, const int64_t* a_strides, const int64_t* b_strides,
                        const int64_t* o_strides, int dtype, void* stream) {
+  FG_REQUIRE_HEALTHY(what);
   FG_REQUIRE(ndim >= 0 && ndim <= 6, "%s: ndim %d not in [0, 6]", what, ndim);
   FG_REQUIRE(ndim == 0 || (sizes && a_strides && b_strides && o_strides), "%s: null shape/stride array", what);
   for (int i = 0; i < ndim; ++i) {

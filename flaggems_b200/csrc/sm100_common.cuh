@@ -16,6 +16,7 @@ enum : int {
   kStatusOk = 0,
   kStatusGemmTimeout = 101,
   kStatusAttnTimeout = 102,
+  kStatusTestTimeout = 103,   // the wait of the test hook fg_debug_wait_timeout
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -62,10 +63,11 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  `abort_flag` lives in shared memory; `status` in global memory.
+// Bounded wait.  `abort_flag` lives in shared memory; `status` is the device status word in
+// global memory, followed (8 bytes on) by a pointer to its host-visible copy, or null.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try(bar, parity)) return true;
   uint64_t t0 = 0;
   uint32_t spins = 0;
@@ -77,9 +79,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicExch(status, code);
+        // the same code into pinned host memory, so that the host learns of it without a sync
+        int* mirror = *reinterpret_cast<int* volatile*>(status + 2);
+        if (mirror != nullptr) {
+          *reinterpret_cast<volatile int*>(mirror) = code;
+          __threadfence_system();
+        }
         return false;
       }
     }

@@ -36,7 +36,8 @@ enum {
   FG_ERR_INVALID = -1,     /* bad argument (shape, stride, dtype, null pointer)   */
   FG_ERR_UNSUPPORTED = -2, /* valid in the reference, not implemented here        */
   FG_ERR_CUDA = -3,        /* a CUDA runtime/driver call failed                   */
-  FG_ERR_TOO_LARGE = -4    /* size exceeds a documented limit of the entry point  */
+  FG_ERR_TOO_LARGE = -4,   /* size exceeds a documented limit of the entry point  */
+  FG_ERR_DEVICE = -5       /* the device status word is set (see fg_device_status): nothing was launched */
 };
 
 /* ABI version of this header; bumped on any signature change. */
@@ -55,9 +56,35 @@ FG_API int fg_set_num_sms(int sms);
 FG_API int fg_get_num_sms(void);
 /* Device status word of the current device: 0 when healthy, otherwise the code a
  * kernel stored when one of its bounded waits (mbarrier / TMEM hand-off) ran out of
- * time and it returned early (101 = GEMM, 102 = attention prefill).  Synchronises
- * with the device (a 4-byte read-back).  reset != 0 clears the word. */
+ * time and it returned early (101 = GEMM, 102 = attention, 103 = the test hook below).
+ * The kernel stores the code in device memory, where every later kernel with bounded waits
+ * reads it and returns at once, and in a word of pinned host memory that each launching
+ * entry point checks first, without synchronising: while the word is set every such entry
+ * point returns FG_ERR_DEVICE and launches nothing, so a caller cannot consume output
+ * buffers that a drained kernel left unwritten without being told.  (The first call that
+ * needs the word on a device page-locks and maps that host word: make one call before
+ * any stream capture.)  The reference has no such state: its kernels have no bounded waits.
+ * fg_device_status synchronises with the device (a 4-byte read-back) and returns the code;
+ * reset != 0 clears both words.  fg_device_status_nosync reads the host word only. */
 FG_API int fg_device_status(int reset);
+FG_API int fg_device_status_nosync(void);
+/* Test hooks (no counterpart in the reference).  fg_debug_set_status stores `code` in both
+ * status words of the current device as a kernel that gave up would (host word only when
+ * there is no device).  fg_debug_wait_timeout enqueues one single-thread kernel that waits,
+ * with the library's bounded wait and a limit of `limit_ns` (at most 100 ms), on an
+ * mbarrier that nothing arrives at -- no copy or MMA is in flight -- and stores in
+ * *outcome_dev (device int) 1 if the wait returned true, 2 if it gave up. */
+FG_API int fg_debug_set_status(int code);
+FG_API int fg_debug_wait_timeout(int64_t limit_ns, int* outcome_dev, void* stream);
+
+/* Strided device-to-device copy of `rows` rows of `width_bytes` on `stream`
+ * (cudaMemcpy2DAsync: DMA engines, no SM).  Source and destination may belong to different
+ * GPUs when the destination is mapped into this process (peer access or symmetric memory).
+ * The multi-GPU layer uses it to push a rank's column shard [M, N/G] into columns
+ * [g N/G, (g+1) N/G) of every peer's row-major [M, N] result.  No counterpart in the
+ * reference (it has no distributed code). */
+FG_API int fg_copy_2d(void* dst, int64_t dst_pitch_bytes, const void* src, int64_t src_pitch_bytes,
+                      int64_t width_bytes, int64_t rows, void* stream);
 
 /* ------------------------------------------------------------------------
  * fused_add_rms_norm: residual += x ; x = rmsnorm(residual) * weight, in place.

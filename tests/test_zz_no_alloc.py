@@ -5,7 +5,10 @@ without an allocator of their own, cannot hand the split-KV kernel a workspace; 
 entry point keeps that scratch in a fixed array inside the library.  Here it is called
 straight through the C ABI, twice in a row (a large batch, then a smaller one, so the
 second call runs over the leftovers of the first), and each result is compared with the
-regular entry point fed a caller-allocated workspace.  Collected last on purpose.
+regular entry point fed a caller-allocated workspace -- the same kernels on the same chunk
+plan, so the comparison is bit for bit -- and once with the CPU oracle.  A further call must
+change neither the free device memory nor launch anything beyond its two kernels.
+Collected last on purpose.
 """
 import ctypes as C
 
@@ -13,9 +16,10 @@ import pytest
 import torch
 
 from flaggems_b200 import _lib, workloads
+from oracle import reference_oracle as O  # checker only
 
 pytestmark = pytest.mark.gpu
-ATOL, RTOL = 2e-2, 1e-2  # the tolerance of the attention parity tests
+ATOL, RTOL = 2e-2, 1e-2  # the tolerance of the attention parity tests (used against the oracle)
 
 
 def _params(b, out, lse):
@@ -66,8 +70,31 @@ def test_decode_static_matches_workspace_entry_point_twice_in_a_row():
     for b in (first, second):
         out_s, lse_s, out_w, lse_w = _run_both(lib, b)
         assert torch.isfinite(out_s).all()
-        torch.testing.assert_close(out_s.float(), out_w.float(), atol=ATOL, rtol=RTOL)
-        torch.testing.assert_close(lse_s, lse_w, atol=ATOL, rtol=RTOL)
+        # same kernels, same chunk plan, only the scratch differs: identical bits
+        assert torch.equal(out_s, out_w)
+        assert torch.equal(lse_s, lse_w)
+    # the second (smaller) batch also against the CPU oracle
+    ref = O.paged_attention(second.q.cpu(), second.key_cache.cpu(), second.value_cache.cpu(), second.query_lens,
+                            second.kv_lens, second.block_table.cpu(), second.scale, compute_dtype=torch.float32)
+    torch.testing.assert_close(out_s.cpu().float(), ref.float(), atol=ATOL, rtol=RTOL)
+
+
+def test_decode_static_call_allocates_nothing_and_launches_two_kernels():
+    lib = _lib.load()
+    b = workloads.decode_batch(seed=34, batch=32, min_ctx=300, max_ctx=5000, device="cuda")
+    out = torch.empty_like(b.q)
+    lse = torch.empty((b.q.shape[1], b.q.shape[0]), dtype=torch.float32, device="cuda")
+    p = _params(b, out, lse)
+    stream = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.fg_flash_attn_decode_static(C.byref(p), stream))   # first touch on this device, if it is
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    launches0 = lib.fg_launch_count()
+    _lib.check(lib.fg_flash_attn_decode_static(C.byref(p), stream))
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, "the call changed the free device memory"
+    assert lib.fg_launch_count() - launches0 == 2   # the split-KV kernel and the combine kernel
 
 
 def test_decode_static_rejects_what_does_not_fit_or_is_not_decode():
@@ -76,7 +103,7 @@ def test_decode_static_rejects_what_does_not_fit_or_is_not_decode():
     out = torch.empty_like(b.q)
     lse = torch.empty((b.q.shape[1], b.q.shape[0]), dtype=torch.float32, device="cuda")
     p = _params(b, out, lse)
-    # a plan far beyond the built-in array: 4096 sequences x 64 heads x 32 chunks
+    # a plan far beyond the built-in array: 4096 sequences x 64 heads x 8 chunks of 1024 tokens
     p.batch = p.total_q = 4096
     p.num_heads, p.num_heads_k = 64, 8
     p.max_seqlen_k = 8192
