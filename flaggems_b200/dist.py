@@ -47,93 +47,124 @@ def column_shard(weight: torch.Tensor, bias, rank: int, world: int):
 
 
 def all_gather_columns(local: torch.Tensor, world: int, group=None, out: torch.Tensor = None) -> torch.Tensor:
-    """Assemble ``[M, N]`` from per-rank column shards ``[M, N/world]``.
+    """Assemble the row-major ``[M, N]`` from per-rank column shards ``[M, N/world]`` with the
+    library collective (NCCL on GPUs, gloo on CPU).
 
-    The collective gathers whole shards (``[world, M, N/world]``, one contiguous
-    message per peer); a strided copy then lays them side by side.  ``out`` may be
-    given to reuse the gather buffer across steps."""
+    The collective gathers whole shards (``[world, M, N/world]``, one contiguous message per
+    peer); a transposing copy (``M x N`` elements, an SM kernel on GPUs) then lays them side by
+    side, into ``out`` when given.  :class:`PeerGather` produces the same matrix without that
+    copy."""
     if world == 1:
         return local
     M, n = local.shape
-    buf = out if out is not None else torch.empty((world * M, n), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(buf.view(world * M, n), local.contiguous(), group=group)
-    return buf.view(world, M, n).permute(1, 0, 2).reshape(M, world * n)
+    tmp = torch.empty((world, M, n), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(tmp.view(world * M, n), local.contiguous(), group=group)
+    if out is None:
+        out = torch.empty((M, world * n), dtype=local.dtype, device=local.device)
+    out.view(M, world, n).copy_(tmp.permute(1, 0, 2))
+    return out
 
 
 class PeerGather:
-    """All-gather of equally shaped shards by copy-engine pushes over NVLink.
+    """All-gather of column shards ``[M, n]`` into the row-major ``[M, world * n]`` matrix by
+    copy-engine pushes over NVLink.
 
     NCCL's all-gather runs on SMs and competes with the compute kernels it is meant to
-    overlap (a persistent GEMM loses whole waves when some SMs are taken).  Here every
-    rank owns a gather buffer ``[world, *shard_shape]`` in symmetric memory
-    (``torch.distributed._symmetric_memory``: the same allocation on every rank, mapped
-    into every peer's address space); ``push`` copies the local shard into slot ``rank``
-    of every peer's buffer with plain device-to-device copies (DMA engines, no SM; about
-    760 GB/s per direction on B200), and ``finish`` closes the round with one tiny NCCL
-    all-reduce on the same stream: when it completes on a rank, every rank has passed
-    its own copies, so all slots of the local buffer are filled.
+    overlap (a persistent GEMM loses whole waves when some SMs are taken), and it delivers
+    ``[world, M, n]``, which still has to be transposed into the matrix the unsharded operator
+    returns.  Here every rank owns the result matrix itself, ``[M, world * n]`` in symmetric
+    memory (``torch.distributed._symmetric_memory``: the same allocation on every rank, mapped
+    into every peer's address space).  The producer writes its shard straight into columns
+    ``[rank * n, (rank + 1) * n)`` of its own matrix (``local_slot``: a strided view, which the
+    GEMM takes as its output), ``push`` copies those columns into the same columns of every
+    peer's matrix with strided device-to-device copies (``fg_copy_2d``: DMA engines, no SM, no
+    multicast; about 760 GB/s per direction on B200), and ``finish`` closes the round with one
+    tiny NCCL all-reduce on the same stream: when it completes on a rank, every rank has passed
+    its own copies, so every column block of the local matrix is filled.  ``columns()`` is that
+    matrix: no copy.
 
-    On CPU tensors (gloo tests) it degrades to ``all_gather_into_tensor``.
-    The caller must not start the next round of pushes before the consumers of the
-    previous result are done with it.
+    ``buffers=2`` keeps two result matrices, so that the pushes of one round may still be in
+    flight while the producer already writes the next round into the other matrix.
+
+    On CPU tensors (gloo tests) it degrades to ``all_gather_into_tensor`` plus the transposing copy.
+    The caller must not reuse a matrix before the consumers of its previous contents, and the
+    ``finish`` of the round that filled it, are done.
     """
 
-    def __init__(self, shard_shape, dtype, device, group=None):
+    def __init__(self, shard_shape, dtype, device, group=None, buffers: int = 1):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.device = torch.device(device)
         self.shard_shape = tuple(shard_shape)
-        self.peer_slots: List[Optional[torch.Tensor]] = [None] * self.world
+        if len(self.shard_shape) != 2:
+            raise ValueError("PeerGather gathers two-dimensional column shards")
+        M, n = self.shard_shape
         self.use_p2p = self.device.type == "cuda" and self.world > 1
-        full = (self.world, *self.shard_shape)
+        full = (M, self.world * n)
+        self.bufs: List[torch.Tensor] = []
+        self.peer_bufs: List[List[Optional[torch.Tensor]]] = []
         if self.use_p2p:
             import torch.distributed._symmetric_memory as symm_mem
 
-            self.buf = symm_mem.empty(full, dtype=dtype, device=self.device)
-            self._handle = symm_mem.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
-            for p in range(self.world):
-                if p != self.rank:
-                    self.peer_slots[p] = self._handle.get_buffer(p, full, dtype)[self.rank]
+            from . import _lib
+
+            self._copy_2d = _lib.load().fg_copy_2d
+            self._check = _lib.check
+            self._handles = []
+            for _ in range(buffers):
+                buf = symm_mem.empty(full, dtype=dtype, device=self.device)
+                handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+                self.bufs.append(buf)
+                self._handles.append(handle)
+                self.peer_bufs.append([None if p == self.rank else handle.get_buffer(p, full, dtype)
+                                       for p in range(self.world)])
             self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
             dist.barrier(group=group)
         else:
-            self.buf = torch.empty(full, dtype=dtype, device=self.device)
+            self.bufs = [torch.empty(full, dtype=dtype, device=self.device) for _ in range(buffers)]
+        self.buf = self.bufs[0]
 
-    def local_slot(self) -> torch.Tensor:
-        """This rank's own slot of the gather buffer: a producer that writes its shard here
-        saves the local copy ``push`` would otherwise make."""
-        return self.buf[self.rank]
+    def local_slot(self, b: int = 0) -> torch.Tensor:
+        """This rank's own columns of result matrix ``b``: a producer that writes its shard
+        here saves the local copy ``push`` would otherwise make."""
+        n = self.shard_shape[1]
+        return self.bufs[b][:, self.rank * n:(self.rank + 1) * n]
 
-    def push(self, local: torch.Tensor, rows: Optional[Tuple[int, int]] = None) -> None:
+    def push(self, local: torch.Tensor, rows: Optional[Tuple[int, int]] = None, b: int = 0) -> None:
         """Enqueue, on the current stream, the copies of ``local`` (or of its rows
-        ``[rows[0], rows[1])``) into every rank's slot.  Pushing a shard in row blocks as
-        they are produced lets the transfer start before the producer has finished."""
-        r0, r1 = rows if rows is not None else (0, self.shard_shape[0])
+        ``[rows[0], rows[1])``) into this rank's columns of every rank's matrix ``b``."""
+        M, n = self.shard_shape
+        r0, r1 = rows if rows is not None else (0, M)
         if not self.use_p2p:
-            if r1 < self.shard_shape[0]:
+            if r1 < M:
                 return  # the collective form moves the whole shard with its last block
             if self.world == 1:
-                self.buf[0].copy_(local)
+                if local.data_ptr() != self.bufs[b].data_ptr():
+                    self.bufs[b].copy_(local)
             else:
-                dist.all_gather_into_tensor(self.buf.view(self.world * self.shard_shape[0], *self.shard_shape[1:]),
-                                            local.contiguous(), group=self.group)
+                all_gather_columns(local, self.world, self.group, out=self.bufs[b])
             return
-        src = local[r0:r1]
-        if local.data_ptr() != self.buf[self.rank].data_ptr():
-            self.buf[self.rank][r0:r1].copy_(src, non_blocking=True)
-        # One stream: copies to the peers follow each other.  Spreading them over one stream per
-        # peer was measured and changes nothing (the rank's total egress stays near 680 GB/s).
-        for i in range(1, self.world):  # staggered so that no peer is hit by everyone at once
+        mine = self.local_slot(b)
+        if local.data_ptr() != mine.data_ptr():
+            mine[r0:r1].copy_(local[r0:r1], non_blocking=True)
+        es = mine.element_size()
+        pitch = mine.stride(0) * es
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        # One stream: the copies to the peers follow each other, staggered so that at any time every
+        # rank sends to one peer and receives from one.  One stream per peer was measured and changes
+        # nothing (a rank's total egress stays near 680-760 GB/s).
+        for i in range(1, self.world):
             p = (self.rank + i) % self.world
-            self.peer_slots[p][r0:r1].copy_(src, non_blocking=True)
+            dst = self.peer_bufs[b][p]
+            self._check(self._copy_2d(dst.data_ptr() + r0 * pitch + self.rank * n * es, pitch,
+                                      mine.data_ptr() + r0 * pitch, pitch, n * es, r1 - r0, stream))
 
     def finish(self) -> None:
-        """Close a round of pushes (current stream): afterwards ``buf`` holds every shard."""
+        """Close a round of pushes (current stream): afterwards the matrix holds every shard."""
         if self.use_p2p:
             dist.all_reduce(self._token, group=self.group)
 
-    def columns(self) -> torch.Tensor:
-        """The gathered ``[M, world * n]`` matrix (a strided view of the buffer)."""
-        M, n = self.shard_shape
-        return self.buf.permute(1, 0, 2).reshape(M, self.world * n)
+    def columns(self, b: int = 0) -> torch.Tensor:
+        """The gathered row-major ``[M, world * n]`` matrix (the buffer itself, no copy)."""
+        return self.bufs[b]

@@ -119,6 +119,7 @@ class PagedBatch:
     # decode only
     new_key: Optional[torch.Tensor] = None
     new_value: Optional[torch.Tensor] = None
+    # int64 cache slot of every new token (decode), or of every packed K/V row (prefill)
     slot_mapping: Optional[torch.Tensor] = None
 
 
@@ -161,7 +162,8 @@ def prefill_batch(seed=0, num_seqs=16, min_len=128, max_len=4096, q_heads=32, kv
     return PagedBatch(q=q, key_cache=kc, value_cache=vc, cu_seqlens_q=cu.to(device),
                       seqused_k=torch.tensor(lens, dtype=torch.int32, device=device),
                       block_table=bt.to(device), query_lens=lens, kv_lens=lens, max_seqlen_q=max(lens),
-                      max_seqlen_k=max(lens), scale=head_dim ** -0.5, k=k, v=v, cu_seqlens_k=cu.to(device))
+                      max_seqlen_k=max(lens), scale=head_dim ** -0.5, k=k, v=v, cu_seqlens_k=cu.to(device),
+                      slot_mapping=slots)
 
 
 def decode_batch(seed=0, batch=256, min_ctx=512, max_ctx=8192, q_heads=32, kv_heads=8, head_dim=128,

@@ -1,40 +1,76 @@
 """Parity against the reference itself on the same GPU: the unmodified FlagGems package
 (installed under ``baseline/_ref``) runs its Triton kernels on the same seeded inputs and
-the results are compared operator by operator with the reference's own tolerances
-(bit-exact for the cache scatter).  Skipped when the reference install is absent or does
-not import (it needs a GPU and Triton)."""
+the results are compared operator by operator -- with the reference's own tolerances, and
+with atol = rtol = 1e-2 (bf16, fp32 accumulation) on top; bit-exact for the cache scatter.
+
+Small cases first, then the benchmark configurations at full size built by
+``flaggems_b200.workloads`` with the benchmark's own seeds: the T=4096 elementwise block,
+all 16 prefill sequences (128..4096 tokens), the batch-256 decode (contexts up to 8192)
+after the cache write, and every row of the four M=8192 projections.  The observed
+maximum absolute / relative errors are written to ``gpurun_out/parity_vs_triton.json``.
+
+Skipped when the reference install is absent or does not import (it needs a GPU and Triton).
+"""
+import json
 import sys
 from pathlib import Path
 
 import pytest
 import torch
 
-from flaggems_b200 import workloads
-from flaggems_b200.testing import assert_close
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from baseline import triton_reference as tref  # noqa: E402
+from flaggems_b200 import workloads  # noqa: E402
+from flaggems_b200.testing import assert_close  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-REF_DIR = Path(__file__).resolve().parent.parent / "baseline" / "_ref"
+TOL = 1e-2  # atol = rtol for bf16 results
+_observed = {}
 
 
 @pytest.fixture(scope="module")
 def ref():
-    if not (REF_DIR / "flag_gems").exists():
-        pytest.skip("reference install baseline/_ref is not present")
-    sys.path.insert(0, str(REF_DIR))
     try:
-        import flag_gems  # the reference, unmodified
-    except Exception as e:  # no GPU, Triton mismatch, ...
-        pytest.skip(f"reference does not import here: {type(e).__name__}: {e}")
-    finally:
-        sys.path.remove(str(REF_DIR))
-    return flag_gems
+        return tref.load()
+    except tref.ReferenceUnavailable as e:
+        pytest.skip(str(e))
 
 
+@pytest.fixture(scope="module", autouse=True)
+def _write_observed():
+    yield
+    if _observed:
+        out = ROOT / "gpurun_out"
+        out.mkdir(exist_ok=True)
+        (out / "parity_vs_triton.json").write_text(json.dumps(_observed, indent=1))
+
+
+def check(name, got, want, atol=TOL, rtol=TOL):
+    """Record max abs / max rel error of `got` against the reference's result and assert
+    |got - want| <= atol + rtol |want| everywhere."""
+    g, w = got.float(), want.float()
+    assert g.shape == w.shape, (name, g.shape, w.shape)
+    err = (g - w).abs()
+    bound = atol + rtol * w.abs()
+    big = w.abs() > 0.05
+    rel = (err[big] / w.abs()[big]).max().item() if big.any() else 0.0
+    bad = int((err > bound).sum().item())
+    _observed[name] = {"max_abs": err.max().item(), "max_rel_where_ref_above_0.05": rel,
+                       "violations_of_1e-2": bad, "elements": g.numel(),
+                       "identical_fraction": float((g == w).float().mean().item())}
+    assert torch.isfinite(g).all(), name
+    assert bad == 0, f"{name}: {bad} of {g.numel()} elements beyond atol={atol}, rtol={rtol}; max abs {err.max().item()}"
+
+
+# ------------------------------------------------------------------------------- small cases
 def test_fused_add_rms_norm_vs_triton(fg, ref):
     x, r, w, eps = workloads.norm_inputs(seed=1, T=512, device=DEV)
     x2, r2 = x.clone(), r.clone()
-    ref.fused_add_rms_norm(x2, r2, [4096], w, eps)
+    tref.call(ref.fused_add_rms_norm, x2, r2, [4096], w, eps)
     fg.fused_add_rms_norm(x, r, [4096], w, eps)
     assert_close(x, x2, torch.bfloat16)
     assert_close(r, r2, torch.bfloat16)
@@ -43,7 +79,7 @@ def test_fused_add_rms_norm_vs_triton(fg, ref):
 def test_rotary_embedding_vs_triton(fg, ref):
     q, k, cos, sin, pos = workloads.rope_inputs(seed=2, T=512, device=DEV)
     for interleaved in (False, True):
-        rq, rk = ref.apply_rotary_pos_emb(q, k, cos, sin, pos, interleaved, False)
+        rq, rk = tref.call(ref.apply_rotary_pos_emb, q, k, cos, sin, pos, interleaved, False)
         oq, ok = fg.apply_rotary_pos_emb(q, k, cos, sin, pos, interleaved, False)
         assert_close(oq, rq, torch.bfloat16)
         assert_close(ok, rk, torch.bfloat16)
@@ -52,13 +88,14 @@ def test_rotary_embedding_vs_triton(fg, ref):
 def test_silu_and_mul_vs_triton(fg, ref):
     x = workloads.silu_inputs(seed=3, T=256, device=DEV)
     d = x.shape[1] // 2
-    assert_close(fg.silu_and_mul(x[:, :d], x[:, d:]), ref.silu_and_mul(x[:, :d], x[:, d:]), torch.bfloat16)
+    assert_close(fg.silu_and_mul(x[:, :d], x[:, d:]), tref.call(ref.silu_and_mul, x[:, :d], x[:, d:]),
+                 torch.bfloat16)
 
 
 def test_reshape_and_cache_flash_vs_triton(fg, ref):
     b = workloads.decode_batch(seed=4, batch=64, min_ctx=16, max_ctx=400, device=DEV)
     kc, vc = b.key_cache.clone(), b.value_cache.clone()
-    ref.reshape_and_cache_flash(b.new_key, b.new_value, kc, vc, b.slot_mapping, "auto", None, None)
+    tref.call(ref.reshape_and_cache_flash, b.new_key, b.new_value, kc, vc, b.slot_mapping, "auto", None, None)
     fg.reshape_and_cache_flash(b.new_key, b.new_value, b.key_cache, b.value_cache, b.slot_mapping, "auto", None, None)
     assert torch.equal(kc, b.key_cache) and torch.equal(vc, b.value_cache)
 
@@ -68,8 +105,8 @@ def test_mm_addmm_vs_triton(fg, ref):
     a = torch.randn(512, 1024, dtype=torch.bfloat16, device=DEV)
     b = torch.randn(1024, 768, dtype=torch.bfloat16, device=DEV) / 32
     bias = torch.randn(768, dtype=torch.bfloat16, device=DEV) * 0.02
-    assert_close(fg.mm(a, b), ref.mm(a, b), torch.bfloat16, reduce_dim=1024)
-    assert_close(fg.addmm(bias, a, b, alpha=0.5, beta=2.0), ref.addmm(bias, a, b, alpha=0.5, beta=2.0),
+    assert_close(fg.mm(a, b), tref.call(ref.mm, a, b), torch.bfloat16, reduce_dim=1024)
+    assert_close(fg.addmm(bias, a, b, alpha=0.5, beta=2.0), tref.call(ref.addmm, bias, a, b, alpha=0.5, beta=2.0),
                  torch.bfloat16, reduce_dim=1024)
 
 
@@ -78,17 +115,16 @@ def test_flash_attn_varlen_prefill_and_decode_vs_triton(fg, ref):
     kw = dict(max_seqlen_q=p.max_seqlen_q, cu_seqlens_q=p.cu_seqlens_q, max_seqlen_k=p.max_seqlen_k,
               seqused_k=p.seqused_k, causal=True, block_table=p.block_table, softmax_scale=p.scale)
     torch.testing.assert_close(fg.flash_attn_varlen_func(p.q, p.key_cache, p.value_cache, **kw).float(),
-                               ref.flash_attn_varlen_func(p.q, p.key_cache, p.value_cache, **kw).float(),
+                               tref.call(ref.flash_attn_varlen_func, p.q, p.key_cache, p.value_cache, **kw).float(),
                                atol=2e-2, rtol=1e-2)
     d = workloads.decode_batch(seed=7, batch=16, min_ctx=30, max_ctx=1500, device=DEV)
     kw = dict(max_seqlen_q=1, cu_seqlens_q=d.cu_seqlens_q, max_seqlen_k=d.max_seqlen_k, seqused_k=d.seqused_k,
               causal=True, block_table=d.block_table, softmax_scale=d.scale)
     torch.testing.assert_close(fg.flash_attn_varlen_func(d.q, d.key_cache, d.value_cache, **kw).float(),
-                               ref.flash_attn_varlen_func(d.q, d.key_cache, d.value_cache, **kw).float(),
+                               tref.call(ref.flash_attn_varlen_func, d.q, d.key_cache, d.value_cache, **kw).float(),
                                atol=2e-2, rtol=1e-2)
 
 
-@pytest.mark.gpu
 def test_get_scheduler_metadata_vs_triton(fg, ref):
     g = torch.Generator().manual_seed(42)
     for b, sk, d, ns, page, knew in [(1, 512, 64, 0, None, 0), (8, 2048, 128, 0, None, 0), (256, 2048, 128, 4, None, 0),
@@ -101,8 +137,93 @@ def test_get_scheduler_metadata_vs_triton(fg, ref):
                   is_causal=False, window_size_left=-1, window_size_right=-1, has_softcap=False, num_splits=ns,
                   pack_gqa=None if page else True, sm_margin=0)
         try:
-            want = ref.get_scheduler_metadata(**kw)
+            want = tref.call(ref.get_scheduler_metadata, **kw)
         except Exception as e:  # the reference's kernels against this image's Triton
             pytest.skip(f"reference get_scheduler_metadata does not run here: {type(e).__name__}: {e}")
         got = fg.get_scheduler_metadata(**kw)
         assert torch.equal(got, want.to(torch.int32)), (b, sk, d, ns, page, knew)
+
+
+# ------------------------------------------------------------- benchmark configurations, full size
+def test_config2_elementwise_block_full_size_vs_triton(fg, ref):
+    """T=4096, hidden 4096: fused_add_rms_norm; rope on q [4096,32,128] / k [4096,8,128];
+    silu_and_mul on the halves of [4096, 22016] (the benchmark's seeds 1, 2, 3)."""
+    x, r, w, eps = workloads.norm_inputs(seed=1, device=DEV)
+    x2, r2 = x.clone(), r.clone()
+    tref.call(ref.fused_add_rms_norm, x2, r2, [4096], w, eps)
+    fg.fused_add_rms_norm(x, r, [4096], w, eps)
+    check("config2/fused_add_rms_norm/out", x, x2)
+    check("config2/fused_add_rms_norm/residual", r, r2)
+    assert_close(x, x2, torch.bfloat16)
+    q, k, cos, sin, pos = workloads.rope_inputs(seed=2, device=DEV)
+    rq, rk = tref.call(ref.apply_rotary_pos_emb, q, k, cos, sin, pos, False, False)
+    oq, ok = fg.apply_rotary_pos_emb(q, k, cos, sin, pos, False, False)
+    check("config2/rotary_embedding/q", oq, rq)
+    check("config2/rotary_embedding/k", ok, rk)
+    q2, k2 = q.clone(), k.clone()
+    fg.apply_rotary_pos_emb(q2, k2, cos, sin, pos, False, True)      # the in-place form the benchmark times
+    assert torch.equal(q2, oq) and torch.equal(k2, ok)
+    act = workloads.silu_inputs(seed=3, device=DEV)
+    d = act.shape[1] // 2
+    want = tref.call(ref.silu_and_mul, act[:, :d], act[:, d:])
+    got = torch.empty_like(want)
+    fg.silu_and_mul_out(act[:, :d], act[:, d:], got)
+    check("config2/silu_and_mul", got, want)
+
+
+def test_config3_prefill_all_sequences_vs_triton(fg, ref):
+    """All 16 sequences (128..4096 tokens) of the benchmark's prefill batch, paged form."""
+    p = workloads.prefill_batch(seed=4, device=DEV)
+    kw = dict(max_seqlen_q=p.max_seqlen_q, cu_seqlens_q=p.cu_seqlens_q, max_seqlen_k=p.max_seqlen_k,
+              seqused_k=p.seqused_k, causal=True, block_table=p.block_table, softmax_scale=p.scale)
+    want = tref.call(ref.flash_attn_varlen_func, p.q, p.key_cache, p.value_cache, **kw)
+    got = fg.flash_attn_varlen_func(p.q, p.key_cache, p.value_cache, **kw)
+    check("config3/prefill_paged", got, want)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=1e-2)
+    # the contiguous form of the same batch (which the reference does not take) must agree with the paged one
+    got_c = fg.flash_attn_varlen_func(p.q, p.k, p.v, p.max_seqlen_q, p.cu_seqlens_q, p.max_seqlen_k,
+                                      cu_seqlens_k=p.cu_seqlens_k, causal=True, softmax_scale=p.scale)
+    check("config3/prefill_contiguous", got_c, want)
+
+
+def test_config4_cache_write_then_decode_batch256_vs_triton(fg, ref):
+    """Batch 256, contexts 512..8192, block 16: the cache write (bit-exact) followed by the
+    decode of one query token per sequence over the written cache."""
+    d = workloads.decode_batch(seed=5, device=DEV)
+    # the reference writes first, into the same caches; the token rows it wrote are kept for the bit comparison
+    slots = d.slot_mapping
+    hk, hd = d.key_cache.shape[2], d.key_cache.shape[3]
+    before_k = d.key_cache.view(-1, hk, hd)[slots].clone()
+    before_v = d.value_cache.view(-1, hk, hd)[slots].clone()
+    tref.call(ref.reshape_and_cache_flash, d.new_key, d.new_value, d.key_cache, d.value_cache, slots, "auto", None, None)
+    ref_k = d.key_cache.view(-1, hk, hd)[slots].clone()
+    ref_v = d.value_cache.view(-1, hk, hd)[slots].clone()
+    d.key_cache.view(-1, hk, hd)[slots] = before_k       # undo, then write with this library
+    d.value_cache.view(-1, hk, hd)[slots] = before_v
+    fg.reshape_and_cache_flash(d.new_key, d.new_value, d.key_cache, d.value_cache, slots, "auto", None, None)
+    assert torch.equal(d.key_cache.view(-1, hk, hd)[slots], ref_k)
+    assert torch.equal(d.value_cache.view(-1, hk, hd)[slots], ref_v)
+    assert torch.equal(ref_k, d.new_key) and torch.equal(ref_v, d.new_value)
+    kw = dict(max_seqlen_q=1, cu_seqlens_q=d.cu_seqlens_q, max_seqlen_k=d.max_seqlen_k, seqused_k=d.seqused_k,
+              causal=True, block_table=d.block_table, softmax_scale=d.scale)
+    want = tref.call(ref.flash_attn_varlen_func, d.q, d.key_cache, d.value_cache, **kw)
+    got = fg.flash_attn_varlen_func(d.q, d.key_cache, d.value_cache, **kw)
+    check("config4/decode_batch256", got, want)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("name", list(workloads.GEMM_SHAPES))
+def test_config5_projection_every_row_vs_triton(fg, ref, name):
+    """M=8192 at the four projection shapes: mm and addmm (bias [N], alpha = beta = 1), all rows."""
+    K, N = workloads.GEMM_SHAPES[name]
+    a, b, bias = workloads.gemm_inputs(name, seed=10 + list(workloads.GEMM_SHAPES).index(name), device=DEV)
+    want = tref.call(ref.mm, a, b)
+    got = fg.mm(a, b)
+    check(f"config5/mm[{name}]", got, want)
+    assert_close(got, want, torch.bfloat16, reduce_dim=K)
+    del want, got
+    want = tref.call(ref.addmm, bias, a, b)
+    with fg.use_gems():
+        got = torch.addmm(bias, a, b)         # through the ATen override
+    check(f"config5/addmm[{name}]", got, want)
+    assert_close(got, want, torch.bfloat16, reduce_dim=K)
