@@ -190,7 +190,8 @@ class Step:
     Only the operators that ``only`` selects get buffers."""
 
     def __init__(self, device, rank: int, world: int, seed: int = 0, small: bool = False, only: str = "",
-                 gather: str = "p2p", op_order: str = "spread", mode: str = "weak", pipeline: bool = True):
+                 gather: str = "p2p", op_order: str = "spread", mode: str = "weak", pipeline: bool = True,
+                 push_streams: int = 1):
         import flaggems_b200 as fg
         from flaggems_b200 import dist as fdist
         from flaggems_b200 import workloads as W
@@ -201,7 +202,7 @@ class Step:
         self.skip_gather = False   # N > 1: second timing of the step without the gathers
         # N > 1: the gathers of step s may still be in flight while step s + 1 computes (two
         # result matrices per projection); a step then waits for the gathers of the step before it
-        self.pipeline = pipeline and world > 1 and gather == "p2p"
+        self.pipeline = pipeline and world > 1 and gather != "nccl"
         self.step_no = 0
         self.fg, self.W, self.fdist = fg, W, fdist
         self.device, self.rank, self.world = device, rank, world
@@ -254,10 +255,15 @@ class Step:
             elif world > 1:  # the full-size shard of a [K, N * world] weight owned by this rank
                 _, b, bias = W.gemm_inputs(name, seed=seed + 10 + i + 100 * (rank + 1), device=device, M=Mg)
             gathered = None
-            if world > 1 and gather != "nccl":
+            if world > 1 and gather == "p2p-slots":
+                # contiguous slot per rank, [world, M, n]: one-dimensional copies, no row-major result
+                gathered = fdist.PeerGatherSlots((a.shape[0], b.shape[1]), a.dtype, device,
+                                                 buffers=2 if self.pipeline else 1)
+                c = [gathered.local_slot(i) for i in range(len(gathered.bufs))]
+            elif world > 1 and gather != "nccl":
                 # the GEMM writes its shard straight into its columns of the row-major result
                 gathered = fdist.PeerGather((a.shape[0], b.shape[1]), a.dtype, device,
-                                            buffers=2 if self.pipeline else 1)
+                                            buffers=2 if self.pipeline else 1, push_streams=push_streams)
                 c = [gathered.local_slot(i) for i in range(len(gathered.bufs))]
             else:
                 c = [torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=device)]
@@ -414,8 +420,8 @@ class Step:
         g = self.gemm[name][4]
         if g is None:
             return self.gemm[name][3][0]
-        if hasattr(g, "columns"):
-            return g.columns(((self.step_no - 1) & 1) if self.pipeline else 0)
+        if hasattr(g, "bufs"):
+            return g.bufs[((self.step_no - 1) & 1) if self.pipeline else 0]
         return g
 
     # ---------------- end-to-end form: host buffers in, host buffers out
@@ -815,10 +821,11 @@ def _workload_config(n_gpus):
         "parallelism": "single GPU" if n_gpus == 1 else
                        f"{n_gpus} ranks, weak scaling: every rank runs the full-size step on its own sequences (no "
                        "exchange); the projections multiply the replicated A by the rank's own full-size column shard "
-                       "and the shards are gathered over NVLink into the row-major [M, ranks x N] result on every rank "
-                       "(copy-engine pushes into peer-mapped buffers + one NCCL all-reduce per step, overlapping the "
-                       "next step's operators; or ncclAllGather with --gather nccl).  The 'tp' key holds the "
-                       "fixed-size step partitioned over the ranks",
+                       "and the shards are gathered over NVLink onto every rank (copy-engine pushes into peer-mapped "
+                       "buffers + one NCCL all-reduce per step, overlapping the next step's operators; --gather picks "
+                       "contiguous slots [ranks, M, N] (default), the row-major [M, ranks x N] written directly, or "
+                       "ncclAllGather).  The 'tp' key holds the fixed-size step partitioned over the ranks, gathered "
+                       "into the row-major [M, N]",
         "l2": "no explicit flush: the step cycles through ~8 GB of operands, every operator's inputs are evicted "
               "from the 126 MB L2 between its consecutive invocations",
     }
@@ -1009,9 +1016,13 @@ def main():
     ap.add_argument("--no-tp", action="store_true", help="N>1: skip the tp leg and the shard check")
     ap.add_argument("--no-pipeline", action="store_true",
                     help="N>1: every step waits for its own gathers (no overlap with the next step)")
-    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
-                    help="N > 1: how the projection shards are gathered (copy-engine pushes into peer-mapped "
-                         "buffers closed by one NCCL all-reduce, or ncclAllGather + transposing copy)")
+    ap.add_argument("--push-streams", type=int, default=1,
+                    help="N>1 with --gather p2p: side streams the copies to the peers are spread over")
+    ap.add_argument("--gather", default="p2p-slots", choices=["p2p", "p2p-slots", "nccl"],
+                    help="N > 1, weak-scaling step: how the projection shards are gathered.  p2p-slots: contiguous "
+                         "copy-engine pushes into one slot per rank ([ranks, M, N]); p2p: strided copy-engine pushes "
+                         "straight into the row-major [M, ranks x N] (what the tp leg always uses; slower beside the "
+                         "compute kernels at 8 ranks); nccl: ncclAllGather + transposing copy")
     ap.add_argument("--op-order", default="spread", choices=["spread", "grouped"],
                     help="order of the operators inside a step: 'spread' puts the short memory-bound operators "
                          "behind the ones that leave little dirty data in L2, 'grouped' runs them by family")
@@ -1055,7 +1066,7 @@ def main():
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         _lib.set_num_sms(sms - NCCL_CTAS)
     step = Step(device, rank, world, small=args.small, only=args.only, gather=args.gather, op_order=args.op_order,
-                pipeline=not args.no_pipeline)
+                pipeline=not args.no_pipeline, push_streams=args.push_streams)
     n_ops = len(step.ops)
 
     def barrier():
@@ -1157,6 +1168,7 @@ def main():
     if world > 1:
         out["no_gather"] = no_gather
         out["all_gather"] = gathers
+        out["config"]["gather"] = args.gather
         out["config"]["gather_pipeline"] = ("the gathers of step s overlap the operators of step s+1 (two result "
                                             "matrices per projection); all K steps' gathers land inside the timed region"
                                             if step.pipeline else "every step waits for its own gathers")
@@ -1188,7 +1200,8 @@ def main():
         # ---- the fixed-size step partitioned over the ranks (strong scaling), under its own key
         chk = shard_check(device, rank, world)
         torch.cuda.empty_cache()
-        tp = Step(device, rank, world, gather="p2p", op_order=args.op_order, mode="tp", pipeline=False)
+        tp = Step(device, rank, world, gather="p2p", op_order=args.op_order, mode="tp", pipeline=False,
+                  push_streams=args.push_streams)
         for _ in range(args.warmup):
             tp.run()
         tp.drain()

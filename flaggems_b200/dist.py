@@ -91,7 +91,7 @@ class PeerGather:
     ``finish`` of the round that filled it, are done.
     """
 
-    def __init__(self, shard_shape, dtype, device, group=None, buffers: int = 1):
+    def __init__(self, shard_shape, dtype, device, group=None, buffers: int = 1, push_streams: int = 1):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -120,6 +120,11 @@ class PeerGather:
                 self.peer_bufs.append([None if p == self.rank else handle.get_buffer(p, full, dtype)
                                        for p in range(self.world)])
             self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+            # push_streams > 1: the copies to different peers are issued on that many side streams, so
+            # that a rank sends to several peers at once and a peer that is momentarily busy with
+            # another sender does not hold up the rank's whole queue
+            self._side = [torch.cuda.Stream(device=self.device) for _ in range(push_streams)] \
+                if push_streams > 1 else []
             dist.barrier(group=group)
         else:
             self.bufs = [torch.empty(full, dtype=dtype, device=self.device) for _ in range(buffers)]
@@ -150,15 +155,25 @@ class PeerGather:
             mine[r0:r1].copy_(local[r0:r1], non_blocking=True)
         es = mine.element_size()
         pitch = mine.stride(0) * es
-        stream = torch.cuda.current_stream(self.device).cuda_stream
-        # One stream: the copies to the peers follow each other, staggered so that at any time every
-        # rank sends to one peer and receives from one.  One stream per peer was measured and changes
-        # nothing (a rank's total egress stays near 680-760 GB/s).
+        cur = torch.cuda.current_stream(self.device)
+        ready = None
+        if self._side:
+            ready = torch.cuda.Event()
+            ready.record(cur)
+            for st in self._side:
+                st.wait_event(ready)
+        # The peers are taken in staggered order (rank + 1, rank + 2, ...), so that ranks in step send to
+        # different peers at any one time.
         for i in range(1, self.world):
             p = (self.rank + i) % self.world
             dst = self.peer_bufs[b][p]
+            st = self._side[(i - 1) % len(self._side)] if self._side else cur
             self._check(self._copy_2d(dst.data_ptr() + r0 * pitch + self.rank * n * es, pitch,
-                                      mine.data_ptr() + r0 * pitch, pitch, n * es, r1 - r0, stream))
+                                      mine.data_ptr() + r0 * pitch, pitch, n * es, r1 - r0, st.cuda_stream))
+        for st in self._side:   # what follows on the current stream (finish) comes after every copy
+            done = torch.cuda.Event()
+            done.record(st)
+            cur.wait_event(done)
 
     def finish(self) -> None:
         """Close a round of pushes (current stream): afterwards the matrix holds every shard."""
@@ -168,3 +183,89 @@ class PeerGather:
     def columns(self, b: int = 0) -> torch.Tensor:
         """The gathered row-major ``[M, world * n]`` matrix (the buffer itself, no copy)."""
         return self.bufs[b]
+
+
+class PeerGatherSlots:
+    """All-gather of equally shaped shards into ``[world, *shard_shape]`` (one contiguous slot per
+    rank) by copy-engine pushes over NVLink: the form with plain one-dimensional copies.
+
+    Same protocol as :class:`PeerGather` (symmetric-memory buffers, the producer writes into
+    ``local_slot``, ``push`` copies it into slot ``rank`` of every peer's buffer, ``finish`` closes
+    the round with one tiny NCCL all-reduce on the same stream), but what a rank receives from a
+    peer is one contiguous block.  On eight B200s stepping through the benchmark, contiguous
+    pushes run at 700-720 GB/s per rank beside the compute kernels where the strided ones of
+    :class:`PeerGather` reach 500-560 GB/s (in isolation both reach 750 GB/s); the price is
+    the layout: the row-major ``[M, world * n]`` matrix takes one more, transposing copy
+    (``columns()``).  ``buffers=2`` keeps two gather buffers for rounds that overlap.
+
+    On CPU tensors (gloo tests) it degrades to ``all_gather_into_tensor``.
+    The caller must not reuse a buffer before the consumers of its previous contents, and the
+    ``finish`` of the round that filled it, are done.
+    """
+
+    def __init__(self, shard_shape, dtype, device, group=None, buffers: int = 1):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.device = torch.device(device)
+        self.shard_shape = tuple(shard_shape)
+        self.use_p2p = self.device.type == "cuda" and self.world > 1
+        full = (self.world, *self.shard_shape)
+        self.bufs: List[torch.Tensor] = []
+        self.peer_slots: List[List[Optional[torch.Tensor]]] = []
+        if self.use_p2p:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            self._handles = []
+            for _ in range(buffers):
+                buf = symm_mem.empty(full, dtype=dtype, device=self.device)
+                handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+                self.bufs.append(buf)
+                self._handles.append(handle)
+                self.peer_slots.append([None if p == self.rank else handle.get_buffer(p, full, dtype)[self.rank]
+                                        for p in range(self.world)])
+            self._token = torch.zeros(1, dtype=torch.float32, device=self.device)
+            dist.barrier(group=group)
+        else:
+            self.bufs = [torch.empty(full, dtype=dtype, device=self.device) for _ in range(buffers)]
+        self.buf = self.bufs[0]
+
+    def local_slot(self, b: int = 0) -> torch.Tensor:
+        """This rank's own slot of gather buffer ``b``: a producer that writes its shard here
+        saves the local copy ``push`` would otherwise make."""
+        return self.bufs[b][self.rank]
+
+    def push(self, local: torch.Tensor, rows: Optional[Tuple[int, int]] = None, b: int = 0) -> None:
+        """Enqueue, on the current stream, the copies of ``local`` (or of its rows
+        ``[rows[0], rows[1])``) into slot ``rank`` of every rank's buffer ``b``."""
+        r0, r1 = rows if rows is not None else (0, self.shard_shape[0])
+        buf = self.bufs[b]
+        if not self.use_p2p:
+            if r1 < self.shard_shape[0]:
+                return  # the collective form moves the whole shard with its last block
+            if self.world == 1:
+                if local.data_ptr() != buf[0].data_ptr():
+                    buf[0].copy_(local)
+            else:
+                dist.all_gather_into_tensor(buf.view(self.world * self.shard_shape[0], *self.shard_shape[1:]),
+                                            local.contiguous(), group=self.group)
+            return
+        src = local[r0:r1]
+        if local.data_ptr() != buf[self.rank].data_ptr():
+            buf[self.rank][r0:r1].copy_(src, non_blocking=True)
+        # One stream: the copies to the peers follow each other, staggered so that ranks in step send
+        # to different peers at any one time.
+        for i in range(1, self.world):
+            p = (self.rank + i) % self.world
+            self.peer_slots[b][p][r0:r1].copy_(src, non_blocking=True)
+
+    def finish(self) -> None:
+        """Close a round of pushes (current stream): afterwards the buffer holds every shard."""
+        if self.use_p2p:
+            dist.all_reduce(self._token, group=self.group)
+
+    def columns(self, b: int = 0) -> torch.Tensor:
+        """The gathered ``[M, world * n]`` matrix: a transposing copy of the slots (M x world x n
+        elements, an SM kernel on GPUs)."""
+        M, n = self.shard_shape
+        return self.bufs[b].permute(1, 0, 2).reshape(M, self.world * n)

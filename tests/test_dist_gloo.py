@@ -36,6 +36,14 @@ def _worker(rank, world, port, ret):
         pg.push(local)
         pg.finish()
         ok_gemm = ok_gemm and torch.allclose(pg.columns(), torch.addmm(bias, a, w), atol=1e-5)
+        ok_gemm = ok_gemm and pg.columns().is_contiguous() and pg.columns().data_ptr() == pg.bufs[0].data_ptr()
+        # the contiguous-slot form, two buffers: [world, M, n] per buffer, columns() transposes
+        ps = fdist.PeerGatherSlots(local.shape, local.dtype, "cpu", buffers=2)
+        for b in (0, 1):
+            ps.push(local * (b + 1), b=b)
+            ps.finish()
+            ok_gemm = ok_gemm and torch.allclose(ps.columns(b), (b + 1) * torch.addmm(bias, a, w), atol=1e-5)
+            ok_gemm = ok_gemm and torch.allclose(ps.bufs[b][rank], (b + 1) * local)
         # attention by KV head: each rank's output slice equals the same slice of the full result
         q = torch.randn(5, 8, 16, generator=g)
         k = torch.randn(5, 4, 16, generator=g)
