@@ -51,8 +51,36 @@ def broadcastable_to(s1, s2) -> bool:
     return True
 
 
+def _tma_ready(x):
+    """A 16-bit matrix in a form the tensor-core kernel can fetch with TMA: 16-byte aligned base
+    and a leading dimension that is a multiple of 8 elements.  A matrix that is not (odd sizes
+    such as K = 1023, or a view that starts mid-row) is copied once into a buffer with the leading
+    dimension rounded up, keeping its row- or column-major order; the padding is never read (the
+    tensor map carries the true extents).  Small operands go to the CUDA-core kernel as they are."""
+    if x.dtype not in (torch.float16, torch.bfloat16) or x.dim() != 2:
+        return x
+    rows, cols = x.shape
+    if rows * cols < 64 * 64:
+        return x
+    col_major = x.stride(0) == 1 and x.stride(1) != 1
+    lead = x.stride(1) if col_major else x.stride(0)
+    unit = x.stride(0) if col_major else x.stride(1)
+    if x.data_ptr() % 16 == 0 and lead % 8 == 0 and lead >= (rows if col_major else cols) and unit == 1:
+        return x
+    if col_major:
+        buf = torch.empty((cols, (rows + 7) // 8 * 8), dtype=x.dtype, device=x.device)
+        out = buf[:, :rows].t()
+    else:
+        buf = torch.empty((rows, (cols + 7) // 8 * 8), dtype=x.dtype, device=x.device)
+        out = buf[:, :cols]
+    out.copy_(x)
+    return out
+
+
 def _gemm(a, b, c, bias=None, alpha=1.0, beta=1.0):
     dev = _lib.require_cuda(a, b, c, bias)
+    if a.shape[0] * b.shape[1] >= 128 * 128 and a.shape[1] >= 32:
+        a, b = _tma_ready(a), _tma_ready(b)
     p = _lib.GemmParams()
     p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
     p.bias = None if bias is None else bias.data_ptr()

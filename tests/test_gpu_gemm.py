@@ -180,3 +180,40 @@ def test_bmm_layouts_and_batches(fg):
     assert_close(fg.bmm(x[:1], y[:1]).cpu(), O.bmm(x[:1].cpu(), y[:1].cpu()), torch.float16, reduce_dim=256)
     assert fg.bmm(x[:0], y[:0]).shape == (0, 128, 128)
     assert _lib.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 1001, 1023), (513, 2049, 999), (2048, 2048, 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b_col", [False, True])
+def test_mm_unaligned_16bit_operands(fg, M, N, K, dtype, b_col):
+    """Odd leading dimensions and views that start mid-row: the host pads such operands once so that
+    the tensor-core kernel takes them; results against the fp64 oracle on every element."""
+    torch.manual_seed(3)
+    a_store = torch.randn((M, K + 3), dtype=dtype, device=DEV)
+    a = a_store[:, 3:]                                   # base not 16-byte aligned, leading dimension K + 3
+    b = torch.randn((N, K), dtype=dtype, device=DEV).t() if b_col else torch.randn((K, N), dtype=dtype, device=DEV)
+    before = _lib.launch_count()
+    res = fg.mm(a, b)
+    assert _lib.launch_count() - before == 1
+    assert res.shape == (M, N) and res.is_contiguous()
+    assert_close(res.cpu(), O.mm(a.cpu(), b.cpu()), dtype, reduce_dim=K)
+    bias = torch.randn((N,), dtype=dtype, device=DEV)
+    with fg.use_gems():
+        res2 = torch.addmm(bias, a, b, alpha=0.5, beta=2.0)
+    assert_close(res2.cpu(), O.addmm(bias.cpu(), a.cpu(), b.cpu(), alpha=0.5, beta=2.0), dtype, reduce_dim=K)
+
+
+@pytest.mark.parametrize("M,N,K", [(1536, 1664, 777), (2048, 1300, 64), (1500, 1536, 1025)])
+@pytest.mark.parametrize("a_col,b_col", [(False, False), (True, True), (False, True)])
+def test_mm_fp32_large_tiles(fg, M, N, K, a_col, b_col):
+    """fp32 (never TF32) on the 128 x 128 CUDA-core tiles, every operand majorness, M/N/K tails;
+    the reference's fp32 tolerance against the fp64 oracle."""
+    torch.manual_seed(4)
+    a = torch.randn((K, M), device=DEV).t() if a_col else torch.randn((M, K), device=DEV)
+    b = torch.randn((N, K), device=DEV).t() if b_col else torch.randn((K, N), device=DEV)
+    res = fg.mm(a, b)
+    assert_close(res.cpu(), O.mm(a.cpu(), b.cpu()), torch.float32, reduce_dim=K)
+    bias = torch.randn((M, N), device=DEV)
+    res2 = fg.addmm(bias, a, b, alpha=-0.999, beta=100.001)
+    assert_close(res2.cpu(), O.addmm(bias.cpu(), a.cpu(), b.cpu(), alpha=-0.999, beta=100.001), torch.float32,
+                 reduce_dim=K)
