@@ -67,7 +67,8 @@ class AttnParams(C.Structure):
             "block_table_stride", "alibi_batch_stride",
             "total_q", "batch", "num_heads", "num_heads_k", "head_dim",
             "max_seqlen_q", "max_seqlen_k", "block_size", "num_blocks",
-            "window_left", "window_right", "total_k")]
+            "window_left", "window_right", "total_k",
+            "q_batch_stride", "k_batch_stride", "v_batch_stride", "o_batch_stride")]
         + [("softmax_scale", C.c_double), ("softcap", C.c_double)]
         + [(n, C.c_int32) for n in ("causal", "dtype", "num_splits", "reserved")]
     )

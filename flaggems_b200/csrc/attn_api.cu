@@ -92,6 +92,20 @@ extern "C" int fg_flash_attn_varlen(const fg_attn_params* p, void* stream) {
   a.bt_stride = p->block_table_stride; a.alibi_bs = p->alibi_batch_stride;
   a.total_q = p->total_q;
   a.total_k = p->total_k;
+  a.q_batch = p->q_batch_stride; a.k_batch = p->k_batch_stride;
+  a.v_batch = p->v_batch_stride; a.o_batch = p->o_batch_stride;
+  a.batch_strided = (p->q_batch_stride | p->k_batch_stride | p->v_batch_stride | p->o_batch_stride) != 0;
+  if (a.batch_strided) {
+    FG_REQUIRE(p->q_batch_stride > 0 && p->k_batch_stride > 0 && p->v_batch_stride > 0 && p->o_batch_stride > 0,
+               "flash_attn_varlen: give all four batch strides or none");
+    FG_REQUIRE(p->q_batch_stride % 8 == 0 && p->k_batch_stride % 8 == 0 && p->v_batch_stride % 8 == 0 &&
+                   p->o_batch_stride % 8 == 0,
+               "flash_attn_varlen: batch strides must be multiples of 8 elements");
+    if (paged || pick_path(p) != kPathPrefillSm100)
+      return fail(FG_ERR_UNSUPPORTED,
+                  "flash_attn_varlen: batch strides are taken by the tensor-core prefill kernel only (head dim 128, "
+                  "contiguous K/V, no ALiBi / soft-cap / window, at least 64 query rows); pack the tensors instead");
+  }
   a.batch = (int)p->batch; a.H = (int)p->num_heads; a.Hk = (int)p->num_heads_k;
   a.group = a.H / a.Hk; a.D = (int)p->head_dim;
   a.max_q = (int)p->max_seqlen_q; a.max_k = (int)p->max_seqlen_k;

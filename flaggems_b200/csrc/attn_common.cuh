@@ -14,6 +14,10 @@ struct AttnArgs {
   int64_t q_rs, q_hs, k_rs, k_hs, k_bs, v_rs, v_hs, v_bs, o_rs, o_hs;
   int64_t bt_stride, alibi_bs;
   int64_t total_q, total_k;
+  // batch-strided dense form (tensor-core prefill kernel only): member b's rows start b * *_batch
+  // elements into the tensor instead of at row cu_seqlens[b]
+  int64_t q_batch, k_batch, v_batch, o_batch;
+  int batch_strided;
   int batch, H, Hk, group, D;
   int max_q, max_k, block_size, num_blocks;
   int wl, wr;         // window, -1 = unbounded (wr == 0 when causal)

@@ -74,7 +74,13 @@ extern "C" __attribute__((visibility("default"))) int fg_debug_read_trace(long l
 namespace fg {
 
 // Ticket counters of the persistent prefill kernel (one per launch in flight, see the launcher).
-constexpr unsigned int kTicketRing = 64;
+// A launch takes the next counter of the ring and zeroes it on its stream ahead of the kernel, so
+// launches on different streams do not share one -- as long as fewer than kTicketRing prefill
+// launches are queued or running on a device at the same time, across all streams (a launch that
+// is still in flight when the ring comes round to its counter would have it zeroed under it and
+// repeat or skip query blocks).  A captured CUDA graph bakes its counter in: do not replay such a
+// graph concurrently with more than kTicketRing - 1 other prefill launches either.
+constexpr unsigned int kTicketRing = 1024;
 __device__ unsigned int g_prefill_tickets[kTicketRing];
 
 int* device_status_ptr();
@@ -286,7 +292,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         mbar_expect_tx(q_full, NT * TILE_BYTES);
         for (int t = 0; t < NT; ++t)
           for (int hf = 0; hf < 2; ++hf)
-            tma_load_3d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmap_q, q_full, hf * 64, it.h0 + t, s.q_begin + it.m0);
+            tma_load_4d(sQ + t * TILE_BYTES + hf * HALF_BYTES, &tmap_q, q_full, hf * 64, it.h0 + t,
+                        a.batch_strided ? it.m0 : s.q_begin + it.m0, a.batch_strided ? it.b : 0);
       }
       ++n_q;
       const int32_t* bt_row = a.paged ? a.block_table + (int64_t)it.b * a.bt_stride : nullptr;
@@ -321,7 +328,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             }
           } else if (lane == 0) {
             for (int hf = 0; hf < 2; ++hf)
-              tma_load_3d(dst + hf * HALF_BYTES, tm, full, hf * 64, hk, s.k_begin + j * BN);
+              tma_load_4d(dst + hf * HALF_BYTES, tm, full, hf * 64, hk,
+                          a.batch_strided ? j * BN : s.k_begin + j * BN, a.batch_strided ? it.b : 0);
           }
         }
       }
@@ -439,7 +447,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       const int qpos = m0 + r;                  // query position inside the sequence
       const bool valid = qpos < s.q_len;
       char* orow = reinterpret_cast<char*>(a.out) +
-                   ((int64_t)(s.q_begin + qpos) * a.o_rs + (int64_t)(it.h0 + t) * a.o_hs) * 2;
+                   ((a.batch_strided ? (int64_t)it.b * a.o_batch + (int64_t)qpos * a.o_rs
+                                     : (int64_t)(s.q_begin + qpos) * a.o_rs) +
+                    (int64_t)(it.h0 + t) * a.o_hs) * 2;
       float* lse_ptr = a.lse ? a.lse + (int64_t)(it.h0 + t) * a.total_q + s.q_begin + qpos : nullptr;
 #ifdef FG_PREFILL_TRACE
       const bool trace_on = blockIdx.x == 0 && g0 == 0 && lane == 0;
@@ -653,11 +663,17 @@ int attn_prefill_sm100(const AttnArgs& a, int dtype, cudaStream_t st) {
   if (!pa.a.status) return fail(FG_ERR_CUDA, "flash_attn_varlen: device status word unavailable");
 
   CUtensorMap tq, tk, tv;
+  // Q and the contiguous K/V are four-dimensional maps [D, heads, rows, batches]: the packed form is
+  // one "batch" of total rows, the batch-strided form (dense batches whose batch and sequence
+  // dimensions do not pack, e.g. a transposed (batch, heads, seq, dim) tensor) has max_seqlen rows
+  // per batch member and the batch stride as the outermost stride.
   {
-    uint64_t dims[3] = {(uint64_t)HD, (uint64_t)a.H, (uint64_t)a.total_q};
-    uint64_t strides[2] = {(uint64_t)a.q_hs * 2, (uint64_t)a.q_rs * 2};
-    uint32_t box[3] = {64, 1, 128};
-    int rc = encode_tmap_16bit(&tq, a.q, 3, dims, strides, box);
+    const uint64_t rows = a.batch_strided ? (uint64_t)a.max_q : (uint64_t)a.total_q;
+    uint64_t dims[4] = {(uint64_t)HD, (uint64_t)a.H, rows, a.batch_strided ? (uint64_t)a.batch : 1ull};
+    uint64_t strides[3] = {(uint64_t)a.q_hs * 2, (uint64_t)a.q_rs * 2,
+                           a.batch_strided ? (uint64_t)a.q_batch * 2 : (uint64_t)a.q_rs * 2 * (rows > 0 ? rows : 1)};
+    uint32_t box[4] = {64, 1, 128, 1};
+    int rc = encode_tmap_16bit(&tq, a.q, 4, dims, strides, box);
     if (rc != FG_OK) return rc;
   }
   if (a.paged) {
@@ -670,13 +686,16 @@ int attn_prefill_sm100(const AttnArgs& a, int dtype, cudaStream_t st) {
     rc = encode_tmap_16bit(&tv, a.v, 4, dims, vs, box);
     if (rc != FG_OK) return rc;
   } else {
-    uint64_t dims[3] = {(uint64_t)HD, (uint64_t)a.Hk, (uint64_t)(a.total_k > 0 ? a.total_k : 1)};
-    uint32_t box[3] = {64, 1, 128};
-    uint64_t ks[2] = {(uint64_t)a.k_hs * 2, (uint64_t)a.k_rs * 2};
-    uint64_t vs[2] = {(uint64_t)a.v_hs * 2, (uint64_t)a.v_rs * 2};
-    int rc = encode_tmap_16bit(&tk, a.k, 3, dims, ks, box);
+    const uint64_t rows = a.batch_strided ? (uint64_t)(a.max_k > 0 ? a.max_k : 1) : (uint64_t)(a.total_k > 0 ? a.total_k : 1);
+    uint64_t dims[4] = {(uint64_t)HD, (uint64_t)a.Hk, rows, a.batch_strided ? (uint64_t)a.batch : 1ull};
+    uint32_t box[4] = {64, 1, 128, 1};
+    uint64_t ks[3] = {(uint64_t)a.k_hs * 2, (uint64_t)a.k_rs * 2,
+                      a.batch_strided ? (uint64_t)a.k_batch * 2 : (uint64_t)a.k_rs * 2 * rows};
+    uint64_t vs[3] = {(uint64_t)a.v_hs * 2, (uint64_t)a.v_rs * 2,
+                      a.batch_strided ? (uint64_t)a.v_batch * 2 : (uint64_t)a.v_rs * 2 * rows};
+    int rc = encode_tmap_16bit(&tk, a.k, 4, dims, ks, box);
     if (rc != FG_OK) return rc;
-    rc = encode_tmap_16bit(&tv, a.v, 3, dims, vs, box);
+    rc = encode_tmap_16bit(&tv, a.v, 4, dims, vs, box);
     if (rc != FG_OK) return rc;
   }
   static thread_local int attr_dev = -1;

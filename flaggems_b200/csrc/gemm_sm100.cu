@@ -401,6 +401,14 @@ static const int g_force_mt = []() {
   return e ? atoi(e) : 0;
 }();
 
+// FLAGGEMS_B200_GEMM_GROUP_MB: megabytes of A rows one group of row tiles may take (default 32; for
+// measurements).
+static const int g_group_mb = []() {
+  const char* e = getenv("FLAGGEMS_B200_GEMM_GROUP_MB");
+  const int v = e ? atoi(e) : 0;
+  return v > 0 ? v : 32;
+}();
+
 // FLAGGEMS_B200_GEMM_SPLIT_TAIL=0 keeps the last wave of 256x256 tiles whole (for measurements).
 static const bool g_split_tail = []() {
   const char* e = getenv("FLAGGEMS_B200_GEMM_SPLIT_TAIL");
@@ -466,7 +474,7 @@ static TilePlan plan_tiles(const fg_gemm_params* p, int64_t batch, int sms, bool
   // (group_m x tile rows x K) around 32 MB, so that it stays L2-resident while B streams
   // through once per group instead of once per few row tiles.
   const int64_t panel = (int64_t)tile_m * p->K * 2;
-  int64_t gm = (32ll << 20) / (panel > 0 ? panel : 1);
+  int64_t gm = ((int64_t)g_group_mb << 20) / (panel > 0 ? panel : 1);
   if (gm < 4) gm = 4;
   if (gm > 64) gm = 64;
   t.group_m = (int)gm;

@@ -404,6 +404,45 @@ def flash_attn_varlen_func(
     return (out, lse) if return_softmax_lse else out
 
 
+def _dense_batch_strided(query, key, value, out, cu_q, cu_k, softmax_scale, causal, wl, wr, softcap, alibi_slopes):
+    """Dense attention on (batch, seq, heads, dim) tensors with arbitrary batch strides through the
+    batch-stride fields of the C ABI.  Returns the lse ``(heads, batch * seq_q)`` or None when the
+    tensor-core prefill kernel, the only one that takes batch strides, does not apply."""
+    if alibi_slopes is not None or softcap or any(x.stride(-1) != 1 for x in (query, key, value)):
+        return None
+    if query.dtype not in (torch.float16, torch.bfloat16) or key.dtype != query.dtype or value.dtype != query.dtype:
+        return None
+    if key.stride() != value.stride():
+        return None
+    B, Sq, H, D = query.shape
+    Sk, Hk = key.shape[1], key.shape[2]
+    dev = _lib.require_cuda(query, key, value, out)
+    lse = torch.empty((H, B * Sq), dtype=torch.float32, device=query.device)
+    p = _lib.AttnParams()
+    p.q, p.k, p.v, p.out, p.lse = query.data_ptr(), key.data_ptr(), value.data_ptr(), out.data_ptr(), lse.data_ptr()
+    p.cu_seqlens_q, p.cu_seqlens_k = cu_q.data_ptr(), cu_k.data_ptr()
+    p.q_batch_stride, p.q_row_stride, p.q_head_stride = query.stride(0), query.stride(1), query.stride(2)
+    p.k_batch_stride, p.k_row_stride, p.k_head_stride = key.stride(0), key.stride(1), key.stride(2)
+    p.v_batch_stride, p.v_row_stride, p.v_head_stride = value.stride(0), value.stride(1), value.stride(2)
+    p.o_batch_stride, p.o_row_stride, p.o_head_stride = Sq * H * D, H * D, D
+    p.total_q, p.total_k, p.batch = B * Sq, B * Sk, B
+    p.num_heads, p.num_heads_k, p.head_dim = H, Hk, D
+    p.max_seqlen_q, p.max_seqlen_k = Sq, Sk
+    p.window_left, p.window_right = wl, wr
+    p.softmax_scale, p.softcap = float(softmax_scale), 0.0
+    p.causal, p.dtype = int(causal), _lib.dtype_code(query.dtype)
+    strides = (p.q_batch_stride, p.q_row_stride, p.q_head_stride, p.k_batch_stride, p.k_row_stride, p.k_head_stride,
+               p.v_batch_stride, p.v_row_stride, p.v_head_stride)
+    if any(st % 8 or st <= 0 for st in strides) or any(x.data_ptr() % 16 for x in (query, key, value)):
+        return None
+    lib = _lib.load()
+    if H % Hk or lib.fg_flash_attn_path(C.byref(p)) != 1:
+        return None
+    with torch.cuda.device(dev):
+        _lib.check(lib.fg_flash_attn_varlen(C.byref(p), _lib.stream_ptr(dev)))
+    return lse
+
+
 _cu_cache: dict = {}
 
 
@@ -450,8 +489,10 @@ def flash_attention_forward(
     same kernels as ``flash_attn_varlen_func`` (tcgen05 prefill for head dim 128, split-KV
     decode for single-token queries, the general kernel otherwise).  Like the reference the
     varlen form of this ATen entry is not supported; unlike it, dropout is not either (this is
-    the inference path) and tensors whose batch and sequence dimensions do not pack (the
-    transposed views SDPA passes) are made contiguous first.
+    the inference path).  Tensors whose batch and sequence dimensions do not pack (the
+    transposed views SDPA passes) go to the tensor-core prefill kernel with their batch
+    strides, as the reference kernel takes them; where that kernel does not apply they are
+    made contiguous first.
     """
     assert cumulative_sequence_length_q is None and cumulative_sequence_length_k is None, \
         "varlen is not supported yet."
@@ -465,19 +506,35 @@ def flash_attention_forward(
     Sk = key.shape[1]
     softmax_scale = scale or 1.0 / (D ** 0.5)
 
-    def packed(x):
+    def packable(x):
         # (batch, seq) -> one token dimension needs stride(0) == seq * stride(1) and unit inner stride
-        if x.stride(-1) == 1 and x.stride(0) == x.shape[1] * x.stride(1):
+        return x.stride(-1) == 1 and x.stride(0) == x.shape[1] * x.stride(1)
+
+    def packed(x):
+        if packable(x):
             return x.as_strided((x.shape[0] * x.shape[1], x.shape[2], x.shape[3]), (x.stride(1), x.stride(2), 1),
                                 x.storage_offset())
         return x.contiguous().view(x.shape[0] * x.shape[1], x.shape[2], x.shape[3])
 
-    q, k, v = packed(query), packed(key), packed(value)
-    out = torch.empty((B * Sq, H, D), dtype=query.dtype, device=query.device)
     wl = -1 if window_size_left is None else int(window_size_left)
     wr = -1 if window_size_right is None else int(window_size_right)
+    out = torch.empty((B * Sq, H, D), dtype=query.dtype, device=query.device)
+    cu_q, cu_k = _dense_cu_seqlens(B, Sq, query.device), _dense_cu_seqlens(B, Sk, query.device)
+    if not (packable(query) and packable(key) and packable(value)):
+        # Tensors whose batch and sequence dimensions do not pack (the transposed views of
+        # (batch, heads, seq, dim) that scaled_dot_product_attention passes): the tensor-core prefill
+        # kernel takes a batch stride, so no copy is needed where it applies.
+        got = _dense_batch_strided(query, key, value, out, cu_q, cu_k, softmax_scale, bool(is_causal), wl, wr,
+                                   softcap, alibi_slopes)
+        if got is not None:
+            lse = got.view(H, B, Sq).permute(1, 0, 2).contiguous()
+            rng_state = torch.zeros(2, dtype=torch.int64, device=query.device)
+            unused = torch.empty(0, dtype=torch.int64, device=query.device)
+            debug_mask = torch.empty(0, dtype=query.dtype, device=query.device)
+            return out.view(B, Sq, H, D), lse, rng_state, unused, debug_mask
+    q, k, v = packed(query), packed(key), packed(value)
     res, lse = flash_attn_varlen_func(
-        q, k, v, Sq, _dense_cu_seqlens(B, Sq, query.device), Sk, cu_seqlens_k=_dense_cu_seqlens(B, Sk, query.device),
+        q, k, v, Sq, cu_q, Sk, cu_seqlens_k=cu_k,
         softmax_scale=softmax_scale, causal=bool(is_causal), window_size=(wl, wr), softcap=softcap,
         alibi_slopes=alibi_slopes, return_softmax_lse=True, out=out)
     lse = lse.view(H, B, Sq).permute(1, 0, 2).contiguous()

@@ -260,6 +260,8 @@ FG_API int fg_gemm_tile_plan(const fg_gemm_params* p, int64_t batch, int num_sms
  *
  * workspace: device scratch for split-KV decode, at least
  * fg_flash_attn_workspace_bytes(...) bytes, or NULL to forbid splitting.
+ * The tensor-core prefill kernel draws its work items from one of 1024 per-device ticket counters,
+ * taken round-robin per launch: keep fewer than 1024 prefill launches in flight per device.
  * ---------------------------------------------------------------------- */
 typedef struct {
   const void* q;
@@ -285,6 +287,16 @@ typedef struct {
   int64_t block_size, num_blocks;
   int64_t window_left, window_right; /* -1 = unbounded */
   int64_t total_k;                   /* rows of k/v in the contiguous form (0 when paged) */
+  /* Batch-strided dense form, all four zero (the packed form) or all four set: batch member b's rows
+   * start b * *_batch_stride elements into q / k / v / out instead of at row cu_seqlens[b], and row i
+   * of the member is i * *_row_stride further on; cu_seqlens_q / cu_seqlens_k still give the lengths
+   * (and the lse columns).  For dense batches whose batch and sequence dimensions do not pack into
+   * one row dimension, such as the (batch, seq, heads, dim) view of a (batch, heads, seq, dim) tensor
+   * that scaled_dot_product_attention passes to aten::_flash_attention_forward (the reference kernel
+   * takes batch strides there, src/flag_gems/ops/flash_api.py:572-916).  Contiguous K/V only, and
+   * only where the tensor-core prefill kernel applies (fg_flash_attn_path == 1), else
+   * FG_ERR_UNSUPPORTED. */
+  int64_t q_batch_stride, k_batch_stride, v_batch_stride, o_batch_stride;
   double softmax_scale;
   double softcap; /* 0 = off */
   int32_t causal;
@@ -320,7 +332,13 @@ FG_API int fg_flash_attn_path(const fg_attn_params* p);
  *    FG_ERR_TOO_LARGE (need = chunks * batch * num_heads * (head_dim + 1) * 4 bytes, with
  *    chunks = ceil(max_seqlen_k / chunk) and chunk between 256 and 1024 tokens);
  *  - the first call on each device looks up the array's device address
- *    (cudaGetSymbolAddress, with that device current) and keeps it;
+ *    (cudaGetSymbolAddress, with that device current) and keeps it; make that call before
+ *    any stream capture;
+ *  - the array is part of the library's device code image, which CUDA loads onto a device at the
+ *    first call into the library there (lazy module loading), not at dlopen: a runtime that hands
+ *    all free device memory to its own pool must make one call into this library on every
+ *    device (any fg_* entry that launches a kernel or resolves a symbol, e.g.
+ *    fg_device_status(0)) BEFORE it does so, or that first call can fail for lack of the 64 MiB;
  *  - all calls on a device share the one array, which keeps whatever the last call
  *    left in it.  Nothing in it has to start at zero (every slot that is read was
  *    written by the same call), but two calls that may run at the same time on one GPU

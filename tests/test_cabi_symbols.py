@@ -48,7 +48,7 @@ def test_struct_sizes_match_the_header():
 
     assert ctypes.sizeof(_lib.RopeParams) == 7 * 8 + 21 * 8 + 4 * 4
     assert ctypes.sizeof(_lib.GemmParams) == 4 * 8 + 11 * 8 + 2 * 8 + 2 * 4
-    assert ctypes.sizeof(_lib.AttnParams) == 11 * 8 + 25 * 8 + 2 * 8 + 4 * 4
+    assert ctypes.sizeof(_lib.AttnParams) == 11 * 8 + 29 * 8 + 2 * 8 + 4 * 4
 
 
 def test_argument_errors_are_reported_without_a_gpu():

@@ -387,6 +387,51 @@ def test_sdpa_through_use_gems_and_gqa(fg):
         fg.flash_attention_forward(qg, kg, vg, None, None, 256, 300, 0.1, True, False)
 
 
+@pytest.mark.parametrize("B,H,Hk,Sq,Sk", [(3, 8, 2, 300, 300), (2, 4, 4, 129, 1000), (2, 16, 8, 1024, 1024)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_flash_attention_forward_batch_strided_views_need_no_copy(fg, B, H, Hk, Sq, Sk, dtype):
+    """(batch, seq, heads, dim) views of (batch, heads, seq, dim) tensors do not pack into one row
+    dimension; the tensor-core kernel takes their batch strides: one launch, no copy kernel, and the
+    same bits as the packed layout gives."""
+    torch.manual_seed(5)
+    q = torch.randn(B, H, Sq, 128, dtype=dtype, device=DEV)
+    k = torch.randn(B, Hk, Sk, 128, dtype=dtype, device=DEV)
+    v = torch.randn(B, Hk, Sk, 128, dtype=dtype, device=DEV)
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    assert qt.stride(0) != Sq * qt.stride(1)
+    before = _lib.launch_count()
+    out, lse, *_ = fg.flash_attention_forward(qt, kt, vt, None, None, Sq, Sk, 0.0, True, False)
+    assert _lib.launch_count() - before == 1
+    out_p, lse_p, *_ = fg.flash_attention_forward(qt.contiguous(), kt.contiguous(), vt.contiguous(), None, None, Sq, Sk,
+                                                  0.0, True, False)
+    assert torch.equal(out, out_p) and torch.equal(lse, lse_p)
+    ref, _ = _sdpa_oracle(q, k.repeat_interleave(H // Hk, dim=1), v.repeat_interleave(H // Hk, dim=1), 128 ** -0.5, True)
+    torch.testing.assert_close(out.transpose(1, 2).cpu().float(), ref, atol=ATOL, rtol=RTOL)
+
+
+def test_batch_strides_are_rejected_where_no_kernel_takes_them(fg):
+    import ctypes as C
+    lib = _lib.load()
+    p = _lib.AttnParams()
+    x = torch.zeros(16, dtype=torch.bfloat16, device=DEV)
+    cu = torch.zeros(3, dtype=torch.int32, device=DEV)
+    p.q = p.k = p.v = p.out = x.data_ptr()
+    p.cu_seqlens_q = p.cu_seqlens_k = cu.data_ptr()
+    p.total_q, p.total_k, p.batch, p.num_heads, p.num_heads_k, p.head_dim = 256, 256, 2, 4, 4, 64   # head dim 64
+    p.max_seqlen_q = p.max_seqlen_k = 128
+    for f in ("q_row_stride", "k_row_stride", "v_row_stride", "o_row_stride"):
+        setattr(p, f, 64)
+    for f in ("q_head_stride", "k_head_stride", "v_head_stride", "o_head_stride"):
+        setattr(p, f, 128 * 64)
+    p.q_batch_stride = p.k_batch_stride = p.v_batch_stride = p.o_batch_stride = 4 * 128 * 64
+    p.window_left = p.window_right = -1
+    p.softmax_scale, p.dtype = 0.125, _lib.dtype_code(torch.bfloat16)
+    assert lib.fg_flash_attn_varlen(C.byref(p), None) == -2          # FG_ERR_UNSUPPORTED, nothing launched
+    p.head_dim = 128
+    p.k_batch_stride = 0
+    assert lib.fg_flash_attn_varlen(C.byref(p), None) == -1          # all four or none
+
+
 # ---------------------------------------------------------------------------------------
 # get_scheduler_metadata: integer work, bit-exact against the fixture recorded from the
 # reference function itself, against the oracle on fresh random inputs, and for the
