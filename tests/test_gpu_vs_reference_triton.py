@@ -7,11 +7,13 @@ Small cases first, then the benchmark configurations at full size built by
 ``flaggems_b200.workloads`` with the benchmark's own seeds: the T=4096 elementwise block,
 all 16 prefill sequences (128..4096 tokens), the batch-256 decode (contexts up to 8192)
 after the cache write, and every row of the four M=8192 projections.  The observed
-maximum absolute / relative errors are written to ``gpurun_out/parity_vs_triton.json``.
+maximum absolute / relative errors are written to the file named by the environment variable
+``FLAGGEMS_B200_PARITY_REPORT`` when it is set.
 
 Skipped when the reference install is absent or does not import (it needs a GPU and Triton).
 """
 import json
+import os
 import sys
 from pathlib import Path
 
@@ -43,10 +45,10 @@ def ref():
 @pytest.fixture(scope="module", autouse=True)
 def _write_observed():
     yield
-    if _observed:
-        out = ROOT / "gpurun_out"
-        out.mkdir(exist_ok=True)
-        (out / "parity_vs_triton.json").write_text(json.dumps(_observed, indent=1))
+    report = os.environ.get("FLAGGEMS_B200_PARITY_REPORT")
+    if _observed and report:
+        Path(report).parent.mkdir(parents=True, exist_ok=True)
+        Path(report).write_text(json.dumps(_observed, indent=1))
 
 
 def check(name, got, want, atol=TOL, rtol=TOL):
