@@ -84,3 +84,17 @@ def test_a_timed_out_wait_reaches_the_host_and_blocks_further_launches(fg):
         _lib.device_status(reset=True)
     assert _lib.device_status_nosync() == 0 and _lib.device_status() == 0
     assert torch.equal(fg.mm(a, b), good)                  # the context is intact and the kernels run again
+    # A launch that is already queued behind the wait when it gives up: the host word was still clear
+    # when it was enqueued, so it is launched; its CTAs read the device word on entry and return
+    # without touching the output (the launch drains instead of running into the same timeout).
+    out = torch.full((256, 256), 7.0, dtype=torch.bfloat16, device=dev)
+    try:
+        _lib.check(lib.fg_debug_wait_timeout(50_000_000, outcome.data_ptr(), _lib.stream_ptr(dev)))
+        fg.mm_out(a, b, out=out)                           # enqueued within the 50 ms the wait lasts
+        torch.cuda.synchronize()
+        assert _lib.device_status_nosync() == 103
+        assert bool((out == 7.0).all()), "a drained launch must not write its output"
+    finally:
+        _lib.device_status(reset=True)
+    fg.mm_out(a, b, out=out)
+    assert torch.equal(out, good)
