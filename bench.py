@@ -202,7 +202,8 @@ class Step:
         self.skip_gather = False   # N > 1: second timing of the step without the gathers
         # N > 1: the gathers of step s may still be in flight while step s + 1 computes (two
         # result matrices per projection); a step then waits for the gathers of the step before it
-        self.pipeline = pipeline and world > 1 and gather != "nccl"
+        self.can_pipeline = world > 1 and gather != "nccl"    # two result buffers per projection exist
+        self.pipeline = bool(pipeline) and self.can_pipeline
         self.step_no = 0
         self.fg, self.W, self.fdist = fg, W, fdist
         self.device, self.rank, self.world = device, rank, world
@@ -258,12 +259,12 @@ class Step:
             if world > 1 and gather == "p2p-slots":
                 # contiguous slot per rank, [world, M, n]: one-dimensional copies, no row-major result
                 gathered = fdist.PeerGatherSlots((a.shape[0], b.shape[1]), a.dtype, device,
-                                                 buffers=2 if self.pipeline else 1)
+                                                 buffers=2 if self.can_pipeline else 1)
                 c = [gathered.local_slot(i) for i in range(len(gathered.bufs))]
             elif world > 1 and gather != "nccl":
                 # the GEMM writes its shard straight into its columns of the row-major result
                 gathered = fdist.PeerGather((a.shape[0], b.shape[1]), a.dtype, device,
-                                            buffers=2 if self.pipeline else 1, push_streams=push_streams)
+                                            buffers=2 if self.can_pipeline else 1, push_streams=push_streams)
                 c = [gathered.local_slot(i) for i in range(len(gathered.bufs))]
             else:
                 c = [torch.empty((a.shape[0], b.shape[1]), dtype=a.dtype, device=device)]
@@ -1014,8 +1015,12 @@ def main():
                          "the leg adds the reference's JIT and autotuning time to the run")
     ap.add_argument("--triton-ref", action="store_true", help="accepted for compatibility: the leg is on by default")
     ap.add_argument("--no-tp", action="store_true", help="N>1: skip the tp leg and the shard check")
-    ap.add_argument("--no-pipeline", action="store_true",
-                    help="N>1: every step waits for its own gathers (no overlap with the next step)")
+    ap.add_argument("--pipeline", default="auto", choices=["auto", "on", "off"],
+                    help="N>1: whether the gathers of a step may overlap the next step's operators.  auto: only when "
+                         "the gathers cannot hide inside their own step (their bytes at 700 GB/s take longer than "
+                         "0.8 x the step without gathers, measured after warm-up): at 8 ranks, not at 2 or 4, where "
+                         "the overlap gains nothing and the copies slow the next step's projections")
+    ap.add_argument("--no-pipeline", action="store_true", help="same as --pipeline off")
     ap.add_argument("--push-streams", type=int, default=1,
                     help="N>1 with --gather p2p: side streams the copies to the peers are spread over")
     ap.add_argument("--gather", default="p2p-slots", choices=["p2p", "p2p-slots", "nccl"],
@@ -1065,8 +1070,10 @@ def main():
     if world > 1 and args.gather == "nccl":
         sms = torch.cuda.get_device_properties(device).multi_processor_count
         _lib.set_num_sms(sms - NCCL_CTAS)
+    if args.no_pipeline:
+        args.pipeline = "off"
     step = Step(device, rank, world, small=args.small, only=args.only, gather=args.gather, op_order=args.op_order,
-                pipeline=not args.no_pipeline, push_streams=args.push_streams)
+                pipeline=args.pipeline == "on", push_streams=args.push_streams)
     n_ops = len(step.ops)
 
     def barrier():
@@ -1078,6 +1085,21 @@ def main():
         step.run()
     step.drain()
     barrier()
+    pipeline_why = None
+    if world > 1 and args.pipeline == "auto" and step.can_pipeline and step.gemm:
+        # can the gathers hide inside their own step?  compare their bytes at 700 GB/s with the step without gathers
+        step.skip_gather = True
+        step.run()
+        ms_c = max_over_ranks(time_steps(step, 2, barrier), device, world) / 2
+        step.skip_gather = False
+        ingress = sum(step.gemm[n][3][0].numel() * 2 for n in step.gemm) * (world - 1)
+        ms_g = ingress / 700e9 * 1e3
+        step.pipeline = ms_g > 0.8 * ms_c
+        pipeline_why = f"gathers {ms_g:.2f} ms at 700 GB/s against {ms_c:.2f} ms of operators per step"
+        for _ in range(2):
+            step.run()
+        step.drain()
+        barrier()
 
     events = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_ops)]
               for _ in range(args.steps)]
@@ -1170,8 +1192,10 @@ def main():
         out["all_gather"] = gathers
         out["config"]["gather"] = args.gather
         out["config"]["gather_pipeline"] = ("the gathers of step s overlap the operators of step s+1 (two result "
-                                            "matrices per projection); all K steps' gathers land inside the timed region"
+                                            "buffers per projection); all K steps' gathers land inside the timed region"
                                             if step.pipeline else "every step waits for its own gathers")
+        if pipeline_why:
+            out["config"]["gather_pipeline"] += f" (chosen after warm-up: {pipeline_why})"
     if world == 1 and not args.small and not args.only:
         if not args.no_triton_ref:
             tr = triton_reference_times(step)
