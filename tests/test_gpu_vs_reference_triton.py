@@ -146,6 +146,36 @@ def test_get_scheduler_metadata_vs_triton(fg, ref):
         assert torch.equal(got, want.to(torch.int32)), (b, sk, d, ns, page, knew)
 
 
+@pytest.mark.parametrize("num_heads", [(4, 4), (8, 2), (16, 2)])
+@pytest.mark.parametrize("head_size", [128, 192, 256])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("alibi,soft_cap", [(False, None), (True, None), (False, 10.0), (False, 50.0)])
+def test_reference_attention_grid_vs_triton(fg, ref, num_heads, head_size, dtype, alibi, soft_cap):
+    """The reference's own varlen grid (tests/test_attention_ops.py:886-995: mixed query lengths,
+    GQA, head dims 128-256, ALiBi, soft-cap; paged cache with random block tables), this time
+    against its Triton kernel instead of the oracle: the kernels behind ALiBi, soft-cap and the
+    other head dims (mma.sync path) are compared with the reference's on the same GPU."""
+    torch.manual_seed(1234567890)
+    seq_lens = [(1, 1328), (5, 18), (129, 463)]
+    qlens, klens = [x[0] for x in seq_lens], [x[1] for x in seq_lens]
+    hq, hk = num_heads
+    block_size, num_blocks = 32, 2048
+    q = torch.randn(sum(qlens), hq, head_size, dtype=dtype, device=DEV)
+    kc = torch.randn(num_blocks, block_size, hk, head_size, dtype=dtype, device=DEV)
+    vc = torch.randn_like(kc)
+    cu = torch.tensor([0] + qlens, dtype=torch.int32).cumsum(0, dtype=torch.int32).to(DEV)
+    used = torch.tensor(klens, dtype=torch.int32, device=DEV)
+    bt = torch.randint(0, num_blocks, (len(seq_lens), (max(klens) + block_size - 1) // block_size), dtype=torch.int32,
+                       device=DEV)
+    slopes = torch.ones(len(seq_lens), hq, dtype=torch.float32, device=DEV) * 0.3 if alibi else None
+    kw = dict(q=q, k=kc, v=vc, cu_seqlens_q=cu, seqused_k=used, max_seqlen_q=max(qlens), max_seqlen_k=max(klens),
+              softmax_scale=head_size ** -0.5, causal=True, window_size=(-1, -1), block_table=bt,
+              softcap=soft_cap if soft_cap is not None else 0, alibi_slopes=slopes, fa_version=2)
+    want = tref.call(ref.flash_attn_varlen_func, **kw)
+    got = fg.flash_attn_varlen_func(**kw)
+    torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=1e-2)
+
+
 # ------------------------------------------------------------- benchmark configurations, full size
 def test_config2_elementwise_block_full_size_vs_triton(fg, ref):
     """T=4096, hidden 4096: fused_add_rms_norm; rope on q [4096,32,128] / k [4096,8,128];
