@@ -176,6 +176,76 @@ def test_reference_attention_grid_vs_triton(fg, ref, num_heads, head_size, dtype
     torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=1e-2)
 
 
+# ------------------------------------------- the reference's own test grids of the other operators
+@pytest.mark.parametrize("shape", [(1, 2), (4096, 256), (200, 40999)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.bfloat16])
+def test_reference_norm_shapes_vs_triton(fg, ref, shape, dtype):
+    """Shapes of tests/test_norm_ops.py:597-632 (the last one takes the two-pass kernel for long rows)."""
+    torch.manual_seed(0)
+    x = torch.randn(shape, dtype=dtype, device=DEV)
+    r = torch.randn(shape, dtype=dtype, device=DEV)
+    w = torch.randn(shape[1:], dtype=dtype, device=DEV)
+    x2, r2 = x.clone(), r.clone()
+    tref.call(ref.fused_add_rms_norm, x2, r2, list(shape[1:]), w, 1e-5)
+    fg.fused_add_rms_norm(x, r, list(shape[1:]), w, 1e-5)
+    assert_close(x, x2, dtype)
+    assert_close(r, r2, dtype)
+
+
+@pytest.mark.parametrize("q_heads,k_heads", [(8, 1), (6, 2), (8, 8)])
+@pytest.mark.parametrize("head_dim", [64, 96, 128, 256])
+@pytest.mark.parametrize("interleaved", [True, False])
+@pytest.mark.parametrize("has_pos_id", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_reference_rope_grid_vs_triton(fg, ref, q_heads, k_heads, head_dim, interleaved, has_pos_id, dtype):
+    """Grid of tests/test_special_ops.py:164-219: 4-D inputs, with position ids or positions = index in the sequence."""
+    torch.manual_seed(0)
+    batch, seq, max_seq = 4, 97, 512
+    q = torch.randn((batch, seq, q_heads, head_dim), dtype=dtype, device=DEV)
+    k = torch.randn((batch, seq, k_heads, head_dim), dtype=dtype, device=DEV)
+    pos = torch.randint(0, max_seq, (batch, seq), device=DEV) if has_pos_id else None
+    cos, sin = workloads.rope_tables(max_seq, head_dim, dtype, DEV)
+    want_q, want_k = tref.call(ref.apply_rotary_pos_emb, q, k, cos, sin, pos, interleaved, False)
+    got_q, got_k = fg.apply_rotary_pos_emb(q, k, cos, sin, pos, interleaved, False)
+    assert_close(got_q, want_q, dtype)
+    assert_close(got_k, want_k, dtype)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 32), (15, 160, 1024), (495, 5333, 71)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("scalar", [-0.999, 100.001])
+def test_reference_blas_grid_vs_triton(fg, ref, M, N, K, dtype, scalar):
+    """Shapes and scalars of tests/test_blas_ops.py:24-92 (tiny, skinny and odd shapes; fp32 without TF32)."""
+    torch.manual_seed(0)
+    a = torch.randn((M, K), dtype=dtype, device=DEV)
+    b = torch.randn((K, N), dtype=dtype, device=DEV)
+    bias = torch.randn((N,), dtype=dtype, device=DEV)
+    assert_close(fg.mm(a, b), tref.call(ref.mm, a, b), dtype, reduce_dim=K)
+    assert_close(fg.addmm(bias, a, b, alpha=scalar, beta=scalar),
+                 tref.call(ref.addmm, bias, a, b, alpha=scalar, beta=scalar), dtype, reduce_dim=K)
+
+
+@pytest.mark.parametrize("head_size", [64, 80, 120, 256])
+@pytest.mark.parametrize("block_size", [8, 16, 32])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_reference_cache_write_grid_vs_triton(fg, ref, head_size, block_size, dtype):
+    """Grid of tests/test_attention_ops.py:1389-1470: 42 tokens into random distinct slots, bit for bit."""
+    import random
+
+    random.seed(2025)
+    torch.manual_seed(2025)
+    num_tokens, num_heads, num_blocks = 42, 8, 1024
+    slots = torch.tensor(random.sample(range(num_blocks * block_size), num_tokens), dtype=torch.long, device=DEV)
+    key = torch.randn((num_tokens, num_heads, head_size), dtype=dtype, device=DEV)
+    value = torch.randn_like(key)
+    kc = torch.randn((num_blocks, block_size, num_heads, head_size), dtype=dtype, device=DEV)
+    vc = torch.randn_like(kc)
+    kc2, vc2 = kc.clone(), vc.clone()
+    tref.call(ref.reshape_and_cache_flash, key, value, kc2, vc2, slots, "auto", None, None)
+    fg.reshape_and_cache_flash(key, value, kc, vc, slots, "auto", None, None)
+    assert torch.equal(kc, kc2) and torch.equal(vc, vc2)
+
+
 # ------------------------------------------------------------- benchmark configurations, full size
 def test_config2_elementwise_block_full_size_vs_triton(fg, ref):
     """T=4096, hidden 4096: fused_add_rms_norm; rope on q [4096,32,128] / k [4096,8,128];
