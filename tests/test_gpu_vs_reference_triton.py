@@ -211,9 +211,9 @@ def test_reference_rope_grid_vs_triton(fg, ref, q_heads, k_heads, head_dim, inte
     assert_close(got_k, want_k, dtype)
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 1, 32), (15, 160, 1024), (495, 5333, 71)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])      # (every shape and dtype costs an autotuning run
-@pytest.mark.parametrize("scalar", [-0.999])                            # of the reference: the grid is kept small)
+@pytest.mark.parametrize("M,N,K,dtype", [(1, 1, 32, torch.bfloat16), (15, 160, 1024, torch.bfloat16),
+                                         (495, 5333, 71, torch.bfloat16), (495, 5333, 71, torch.float32)])
+@pytest.mark.parametrize("scalar", [-0.999])   # (every shape and dtype costs an autotuning run of the reference: kept small)
 def test_reference_blas_grid_vs_triton(fg, ref, M, N, K, dtype, scalar):
     """Shapes and scalars of tests/test_blas_ops.py:24-92 (tiny, skinny and odd shapes; fp32 without TF32)."""
     torch.manual_seed(0)
