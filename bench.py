@@ -598,12 +598,13 @@ def extra_op_times(device, peaks, reps=10, full=False):
         with torch.no_grad():
             ms = timed_median(lambda: fg.gelu_and_mul(x[:, :half], x[:, half:], approximate), flush, reps)
         entry(f"gelu_and_mul[{approximate}] halves of [4096, 22016] (incl. output allocation)", ms, nbytes, "hbm")
-    # fp32 mm (never TF32): the CUDA-core kernel that serves what the tensor-core path does not take
+    # fp32 mm (never TF32): at this size three bf16 pieces per operand on the tensor cores, chunked accumulation
     a32 = torch.randn((4096, 4096), generator=g, dtype=torch.float32).to(device)
     b32 = torch.randn((4096, 4096), generator=g, dtype=torch.float32).to(device)
     ms = timed_median(lambda: fg.mm(a32, b32), flush, max(3, reps // 3), warm=1)
     out.append({"op": "mm fp32 4096 x 4096 x 4096 (no TF32; incl. output allocation)", "ms": round(ms, 4),
-                "bound": "fp32 pipe", "achieved": round(2 * 4096 ** 3 / ms / 1e9, 1), "unit": "TFLOP/s"})
+                "bound": "tensor (six bf16 piece products per fp32 product)", "achieved": round(2 * 4096 ** 3 / ms / 1e9, 1),
+                "unit": "TFLOP/s"})
     return out
 
 

@@ -122,6 +122,8 @@ SIGNATURES = {
     "fg_gemm": (C.c_int, [C.POINTER(GemmParams), _P]),
     "fg_gemm_batched": (C.c_int, [C.POINTER(GemmParams)] + [_I64] * 5 + [_P]),
     "fg_gemm_uses_tcgen05": (C.c_int, [C.POINTER(GemmParams)]),
+    "fg_gemm_f32_split_workspace_bytes": (_I64, [C.POINTER(GemmParams)]),
+    "fg_gemm_f32_split": (C.c_int, [C.POINTER(GemmParams), _P, _I64, _P]),
     "fg_gemm_tile_plan": (C.c_int, [C.POINTER(GemmParams), _I64, C.c_int, C.POINTER(GemmPlan)]),
     "fg_flash_attn_varlen": (C.c_int, [C.POINTER(AttnParams), _P]),
     "fg_flash_attn_workspace_bytes": (C.c_int64, [_I64] * 5),

@@ -23,10 +23,12 @@ struct GArgs {
   int64_t as0, as1, bs0, bs1, cs0, cs1, zs0, zs1;
   float alpha, beta;
   int has_bias;
+  const int* only_if;   // null, or a device flag: the launch does nothing while it is zero
 };
 
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_generic_kernel(GArgs g) {
+  if (g.only_if != nullptr && *g.only_if == 0) return;
   __shared__ float sa[TK][TM + 4];
   __shared__ float sb[TK][TN + 4];
   const T* A = reinterpret_cast<const T*>(g.a);
@@ -118,6 +120,7 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 
 template <typename T>
 __global__ void __launch_bounds__(256, FG_SIMT128_MIN_CTAS) gemm_simt128_kernel(GArgs g) {
+  if (g.only_if != nullptr && *g.only_if == 0) return;
   __shared__ __align__(16) float sa[BTK][BTM + 4];
   __shared__ __align__(16) float sb[BTK][BTN + 4];
   const T* A = reinterpret_cast<const T*>(g.a);
@@ -222,8 +225,9 @@ extern "C" int fg_gemm_uses_tcgen05(const fg_gemm_params* p) {
 }
 
 namespace fg {
-static int gemm_one(const fg_gemm_params* p, cudaStream_t st) {
+static int gemm_one(const fg_gemm_params* p, cudaStream_t st, const int* only_if = nullptr) {
   GArgs g;
+  g.only_if = only_if;
   g.a = p->a; g.b = p->b; g.bias = p->bias; g.c = p->c;
   g.M = p->M; g.N = p->N; g.K = p->K;
   g.as0 = p->a_stride0; g.as1 = p->a_stride1; g.bs0 = p->b_stride0; g.bs1 = p->b_stride1;
@@ -247,6 +251,11 @@ static int gemm_one(const fg_gemm_params* p, cudaStream_t st) {
   return FG_OK;
 }
 
+// The CUDA-core kernel for `p`, gated on a device flag: its CTAs return at once while the flag is zero.
+int gemm_simt_gated(const fg_gemm_params* p, const int* only_if_nonzero, cudaStream_t st) {
+  return gemm_one(p, st, only_if_nonzero);
+}
+
 static int gemm_checked(const char* what, const fg_gemm_params* p) {
   FG_REQUIRE(p != nullptr, "%s: null params", what);
   FG_REQUIRE(p->M >= 0 && p->N >= 0 && p->K >= 0, "%s: negative size", what);
@@ -265,6 +274,21 @@ extern "C" int fg_gemm(const fg_gemm_params* p, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (gemm_tcgen05_eligible(p)) return gemm_tcgen05(p, GemmBatch(), st);
   return gemm_one(p, st);
+}
+
+namespace fg {
+int64_t gemm_f32_split_workspace_bytes(const fg_gemm_params* p);
+int gemm_f32_split(const fg_gemm_params* p, void* workspace, int64_t workspace_bytes, cudaStream_t st);
+}
+extern "C" int64_t fg_gemm_f32_split_workspace_bytes(const fg_gemm_params* p) {
+  return fg::gemm_f32_split_workspace_bytes(p);
+}
+extern "C" int fg_gemm_f32_split(const fg_gemm_params* p, void* workspace, int64_t workspace_bytes, void* stream) {
+  using namespace fg;
+  FG_REQUIRE_HEALTHY("gemm_f32_split");
+  const int rc = gemm_checked("gemm_f32_split", p);
+  if (rc != FG_OK) return rc < 0 ? rc : FG_OK;
+  return gemm_f32_split(p, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 extern "C" int fg_gemm_batched(const fg_gemm_params* p, int64_t batch, int64_t a_batch_stride,

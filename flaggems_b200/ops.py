@@ -11,6 +11,7 @@ from __future__ import annotations
 import ctypes as C
 import logging
 import math
+import os
 
 import torch
 
@@ -49,6 +50,10 @@ def broadcastable_to(s1, s2) -> bool:
         if s1[-i] != 1 and s1[-i] != s2[-i]:
             return False
     return True
+
+
+# FLAGGEMS_B200_F32_SPLIT=0 keeps fp32 matrix products on the CUDA-core kernel (for measurements).
+_F32_SPLIT = os.environ.get("FLAGGEMS_B200_F32_SPLIT", "1") != "0"
 
 
 def _tma_ready(x):
@@ -93,8 +98,18 @@ def _gemm(a, b, c, bias=None, alpha=1.0, beta=1.0):
         p.bias_stride0, p.bias_stride1 = bias.stride()
     p.alpha, p.beta = float(alpha), float(beta)
     p.dtype = _lib.dtype_code(c.dtype)
+    lib = _lib.load()
     with torch.cuda.device(dev):
-        _lib.check(_lib.load().fg_gemm(C.byref(p), _lib.stream_ptr(dev)))
+        # Large fp32 problems run on the tensor cores from three bf16 pieces per operand (fp32-level
+        # error, never TF32); the pieces live in a scratch buffer for the duration of the call.
+        need = lib.fg_gemm_f32_split_workspace_bytes(C.byref(p)) if c.dtype == torch.float32 and _F32_SPLIT else 0
+        if need > 0:
+            scratch = torch.empty(need, dtype=torch.uint8, device=c.device)
+            _lib.check(lib.fg_gemm_f32_split(C.byref(p), scratch.data_ptr(), need, _lib.stream_ptr(dev)))
+            # (freed on return: the caching allocator hands the block out again only to work queued
+            # behind this call on the same stream)
+        else:
+            _lib.check(lib.fg_gemm(C.byref(p), _lib.stream_ptr(dev)))
     return c
 
 

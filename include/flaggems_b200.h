@@ -227,6 +227,21 @@ FG_API int fg_gemm(const fg_gemm_params* p, void* stream);
 FG_API int fg_gemm_batched(const fg_gemm_params* p, int64_t batch, int64_t a_batch_stride,
                            int64_t b_batch_stride, int64_t c_batch_stride, int64_t bias_batch_stride,
                            void* stream);
+/* fp32 problems on the tensor cores, never TF32 (the reference multiplies fp32 with
+ * allow_tf32=False, src/flag_gems/ops/mm.py:100-107, src/flag_gems/ops/addmm.py:60-66): each operand is
+ * written into `workspace` as three bf16 pieces that add up to it exactly, six piece products are
+ * accumulated by tcgen05.mma in short K chunks, and the chunks are added in fp32 with round to
+ * nearest.  Error against fp64 is at or below that of an fp32 FMA loop.  If an input holds an
+ * infinity or a NaN the CUDA-core kernel computes the result instead (decided on the device, no
+ * host synchronisation), so special values propagate as in fp32 arithmetic.
+ * fg_gemm_f32_split_workspace_bytes: bytes of scratch the call needs, or 0 when the problem does
+ * not qualify (dtype other than fp32, a dimension below 128, M*N*K below 2^29, an operand without
+ * a unit stride, c_stride1 != 1) and fg_gemm should be called.  Pure host logic.
+ * fg_gemm_f32_split: `workspace` is device memory, 256-byte aligned, of at least that many bytes,
+ * owned by the call until the work queued on `stream` has run.  FG_ERR_UNSUPPORTED when the
+ * problem does not qualify. */
+FG_API int64_t fg_gemm_f32_split_workspace_bytes(const fg_gemm_params* p);
+FG_API int fg_gemm_f32_split(const fg_gemm_params* p, void* workspace, int64_t workspace_bytes, void* stream);
 /* 1 if fg_gemm would take the tcgen05/TMA path for these arguments, 0 if the
  * generic path.  Pure host logic (no CUDA call). */
 FG_API int fg_gemm_uses_tcgen05(const fg_gemm_params* p);

@@ -25,6 +25,7 @@ def test_every_launching_entry_point_refuses_while_the_word_is_set():
         z = C.c_int64(0)
         calls = {
             "fg_gemm": lambda: lib.fg_gemm(C.byref(_lib.GemmParams()), None),
+            "fg_gemm_f32_split": lambda: lib.fg_gemm_f32_split(C.byref(_lib.GemmParams()), None, 0, None),
             "fg_gemm_batched": lambda: lib.fg_gemm_batched(C.byref(_lib.GemmParams()), 1, 0, 0, 0, 0, None),
             "fg_flash_attn_varlen": lambda: lib.fg_flash_attn_varlen(C.byref(_lib.AttnParams()), None),
             "fg_flash_attn_decode_static": lambda: lib.fg_flash_attn_decode_static(C.byref(_lib.AttnParams()), None),

@@ -205,9 +205,11 @@ def test_mm_unaligned_16bit_operands(fg, M, N, K, dtype, b_col):
 
 @pytest.mark.parametrize("M,N,K", [(1536, 1664, 777), (2048, 1300, 64), (1500, 1536, 1025)])
 @pytest.mark.parametrize("a_col,b_col", [(False, False), (True, True), (False, True)])
-def test_mm_fp32_large_tiles(fg, M, N, K, a_col, b_col):
+def test_mm_fp32_large_tiles(fg, M, N, K, a_col, b_col, monkeypatch):
     """fp32 (never TF32) on the 128 x 128 CUDA-core tiles, every operand majorness, M/N/K tails;
     the reference's fp32 tolerance against the fp64 oracle."""
+    from flaggems_b200 import ops
+    monkeypatch.setattr(ops, "_F32_SPLIT", False)      # keep these shapes on the CUDA-core kernel
     torch.manual_seed(4)
     a = torch.randn((K, M), device=DEV).t() if a_col else torch.randn((M, K), device=DEV)
     b = torch.randn((N, K), device=DEV).t() if b_col else torch.randn((K, N), device=DEV)
@@ -217,3 +219,105 @@ def test_mm_fp32_large_tiles(fg, M, N, K, a_col, b_col):
     res2 = fg.addmm(bias, a, b, alpha=-0.999, beta=100.001)
     assert_close(res2.cpu(), O.addmm(bias.cpu(), a.cpu(), b.cpu(), alpha=-0.999, beta=100.001), torch.float32,
                  reduce_dim=K)
+
+
+def _split_bytes(a, b, c):
+    p = _lib.GemmParams()
+    p.a, p.b, p.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    p.M, p.K = a.shape
+    p.N = b.shape[1]
+    p.a_stride0, p.a_stride1 = a.stride()
+    p.b_stride0, p.b_stride1 = b.stride()
+    p.c_stride0, p.c_stride1 = c.stride()
+    p.dtype = _lib.dtype_code(c.dtype)
+    return int(_lib.load().fg_gemm_f32_split_workspace_bytes(ctypes.byref(p)))
+
+
+def _err(x, ref):
+    d = (x.double() - ref).abs()
+    return float(d.mean() / ref.abs().mean()), float(d.max() / ref.abs().max())
+
+
+@pytest.mark.parametrize("M,N,K", [(1536, 1664, 777), (1000, 1111, 1300), (640, 2048, 4096), (129, 8200, 600)])
+@pytest.mark.parametrize("a_col,b_col", [(False, False), (True, True), (False, True), (True, False)])
+def test_mm_fp32_tensor_core_split(fg, M, N, K, a_col, b_col):
+    """Large fp32 products on the tensor cores from three bf16 pieces per operand: every operand
+    majorness, M/N/K tails.  The error against fp64 must stay at the level of an fp32 FMA loop
+    (here: ATen's fp32 GEMM with TF32 off), not merely inside the reference's loose tolerance."""
+    torch.manual_seed(5)
+    a = torch.randn((K, M), device=DEV).t() if a_col else torch.randn((M, K), device=DEV)
+    b = torch.randn((N, K), device=DEV).t() if b_col else torch.randn((K, N), device=DEV)
+    assert _split_bytes(a, b, torch.empty((M, N), device=DEV)) > 0
+    ref = a.double() @ b.double()
+    res = fg.mm(a, b)
+    assert_close(res.cpu(), ref.cpu(), torch.float32, reduce_dim=K)
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        aten = torch.mm(a, b)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    mean_fg, max_fg = _err(res, ref)
+    mean_at, max_at = _err(aten, ref)
+    assert mean_fg <= 1.25 * mean_at + 1e-8, (mean_fg, mean_at)
+    assert max_fg <= 2.0 * max_at + 1e-7, (max_fg, max_at)
+    # addmm: full bias matrix and a row vector, scalars of the reference's grid
+    bias = torch.randn((M, N), device=DEV)
+    res2 = fg.addmm(bias, a, b, alpha=-0.999, beta=100.001)
+    assert_close(res2.cpu(), O.addmm(bias.cpu(), a.cpu(), b.cpu(), alpha=-0.999, beta=100.001), torch.float32,
+                 reduce_dim=K)
+    row = torch.randn((N,), device=DEV)
+    res3 = fg.addmm(row, a, b, alpha=0.001, beta=-111.999)
+    assert_close(res3.cpu(), O.addmm(row.cpu(), a.cpu(), b.cpu(), alpha=0.001, beta=-111.999), torch.float32,
+                 reduce_dim=K)
+
+
+def test_mm_fp32_split_same_signed_data_and_output_views(fg):
+    """Same-signed data is where a truncating accumulator shows: one tensor-core accumulator over
+    K = 4096 is low by 1e-5 of the result; the chunked sums must stay below 1.5e-6.  Also an output
+    view that allows no 16-byte stores."""
+    torch.manual_seed(6)
+    M, N, K = 512, 1024, 4096
+    a = torch.rand((M, K), device=DEV)
+    b = torch.rand((K, N), device=DEV)
+    ref = a.double() @ b.double()
+    res = fg.mm(a, b)
+    rel = (res.double() - ref) / ref
+    assert float(rel.abs().max()) < 1.5e-6, float(rel.abs().max())
+    assert abs(float(rel.mean())) < 1.0e-6, float(rel.mean())
+    buf = torch.full((M, N + 3), 7.0, device=DEV)
+    out = buf[:, 1:N + 1]                       # rows start 4 bytes off a 16-byte boundary, odd pitch
+    assert _split_bytes(a, b, out) > 0
+    fg.mm_out(a, b, out=out)
+    assert torch.equal(out, res)
+    assert bool((buf[:, 0] == 7.0).all()) and bool((buf[:, N + 1:] == 7.0).all())
+
+
+def test_mm_fp32_split_special_values(fg, monkeypatch):
+    """An infinity or a NaN among the inputs: the pieces cannot carry it (inf times a zero piece
+    is NaN), so the device-side flag hands the whole product to the CUDA-core kernel and the
+    result is that kernel's, bit for bit."""
+    from flaggems_b200 import ops
+    torch.manual_seed(7)
+    M, N, K = 512, 1024, 1024
+    a = torch.randn((M, K), device=DEV)
+    b = torch.randn((K, N), device=DEV)
+    a[3, 5] = float("inf")
+    b[7, 9] = float("nan")
+    a[100, 0] = 3.4e38                             # rounds past the largest finite bf16: still finite
+    assert _split_bytes(a, b, torch.empty((M, N), device=DEV)) > 0
+    res = fg.mm(a, b)
+    monkeypatch.setattr(ops, "_F32_SPLIT", False)
+    simt = fg.mm(a, b)
+    assert torch.equal(torch.nan_to_num(res, nan=1.5, posinf=2.5, neginf=-2.5),
+                       torch.nan_to_num(simt, nan=1.5, posinf=2.5, neginf=-2.5))
+    assert bool(torch.isinf(res[3]).any()) and bool(torch.isnan(res[:, 9]).all())
+    # finite but huge values stay on the tensor cores and come out right
+    monkeypatch.setattr(ops, "_F32_SPLIT", True)
+    a2 = torch.randn((M, K), device=DEV)
+    a2[100, 0] = 3.4e38
+    b2 = torch.randn((K, N), device=DEV) * 1e-3
+    r2 = fg.mm(a2, b2)
+    ref2 = a2.double() @ b2.double()
+    assert bool(torch.isfinite(r2).all())
+    assert float(((r2.double() - ref2).abs() / ref2.abs().max()).max()) < 1e-6

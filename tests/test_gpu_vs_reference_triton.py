@@ -225,6 +225,21 @@ def test_reference_blas_grid_vs_triton(fg, ref, M, N, K, dtype, scalar):
                  tref.call(ref.addmm, bias, a, b, alpha=scalar, beta=scalar), dtype, reduce_dim=K)
 
 
+def test_fp32_mm_on_tensor_cores_is_as_accurate_as_the_reference(fg, ref):
+    """A large fp32 product: the reference multiplies with `allow_tf32=False` (ops/mm.py:100-107); here it
+    runs on the tensor cores from three bf16 pieces per operand.  Both against fp64: the error of
+    this library's result must not exceed the reference's."""
+    torch.manual_seed(0)
+    M = N = K = 2048
+    a = torch.randn((M, K), dtype=torch.float32, device=DEV)
+    b = torch.randn((K, N), dtype=torch.float32, device=DEV)
+    exact = a.double() @ b.double()
+    got, want = fg.mm(a, b), tref.call(ref.mm, a, b)
+    assert_close(got, want, torch.float32, reduce_dim=K)
+    err = lambda x: float((x.double() - exact).abs().mean() / exact.abs().mean())
+    assert err(got) <= err(want) * 1.1 + 1e-8, (err(got), err(want))
+
+
 @pytest.mark.parametrize("head_size", [64, 80, 120, 256])
 @pytest.mark.parametrize("block_size", [8, 16, 32])
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])

@@ -109,6 +109,29 @@ def test_gemm_path_selection_is_pure_host_logic():
     assert uses(_gemm_params(8192, 6144, 4096, base=0x7f0000000002)) == 0       # misaligned base
 
 
+def test_f32_split_workspace_is_pure_host_logic():
+    """fg_gemm_f32_split_workspace_bytes: 0 when fg_gemm should take the problem, else a 256-byte
+    flag block plus three bf16 pieces per operand with the leading dimension rounded up to 8."""
+    need = lambda p: _lib.load().fg_gemm_f32_split_workspace_bytes(ctypes.byref(p))
+    up = lambda v, m: (v + m - 1) // m * m
+    f32 = _lib.FG_F32
+    assert need(_gemm_params(4096, 4096, 4096, dtype=f32)) == 256 + 2 * 3 * 4096 * 4096 * 2
+    # odd sizes: A [1000, 1300] row-major -> 1000 rows of 1304; B [1300, 1111] row-major -> 1300 rows of 1112
+    assert need(_gemm_params(1000, 1111, 1300, dtype=f32)) == 256 + up(3 * 1000 * 1304 * 2, 256) + up(3 * 1300 * 1112 * 2, 256)
+    # column-major A [1000, 1300] (stride0 == 1): 1300 rows of 1000
+    assert need(_gemm_params(1000, 1111, 1300, dtype=f32, a_strides=(1, 1000))) == \
+        256 + up(3 * 1300 * 1000 * 2, 256) + up(3 * 1300 * 1112 * 2, 256)
+    assert need(_gemm_params(4096, 4096, 4096)) == 0                              # bf16: fg_gemm's tensor-core kernel
+    assert need(_gemm_params(512, 1024, 512, dtype=f32)) == 0                     # M*N*K below 2^29
+    assert need(_gemm_params(512, 1024, 1024, dtype=f32)) > 0
+    assert need(_gemm_params(4096, 4096, 127, dtype=f32)) == 0                    # a dimension below 128
+    assert need(_gemm_params(4096, 4096, 4096, dtype=f32, a_strides=(8192, 2))) == 0   # no unit stride
+    p = _gemm_params(4096, 4096, 4096, dtype=f32)
+    p.c_stride0, p.c_stride1 = 1, 4096
+    assert need(p) == 0                                                           # column-major output
+    assert _lib.load().fg_gemm_f32_split(ctypes.byref(p), None, 0, None) == -2    # FG_ERR_UNSUPPORTED, nothing launched
+
+
 def test_attention_path_selection():
     def params(max_q, batch, total_q, hq=32, hk=8, d=128, alibi=False, wl=-1):
         p = _lib.AttnParams()
