@@ -103,8 +103,13 @@ def _gemm(a, b, c, bias=None, alpha=1.0, beta=1.0):
         # Large fp32 problems run on the tensor cores from three bf16 pieces per operand (fp32-level
         # error, never TF32); the pieces live in a scratch buffer for the duration of the call.
         need = lib.fg_gemm_f32_split_workspace_bytes(C.byref(p)) if c.dtype == torch.float32 and _F32_SPLIT else 0
+        scratch = None
         if need > 0:
-            scratch = torch.empty(need, dtype=torch.uint8, device=c.device)
+            try:
+                scratch = torch.empty(need, dtype=torch.uint8, device=c.device)
+            except torch.cuda.OutOfMemoryError:
+                scratch = None      # no room for the pieces (1.5 x the operands): the CUDA-core kernel needs none
+        if scratch is not None:
             _lib.check(lib.fg_gemm_f32_split(C.byref(p), scratch.data_ptr(), need, _lib.stream_ptr(dev)))
             # (freed on return: the caching allocator hands the block out again only to work queued
             # behind this call on the same stream)
