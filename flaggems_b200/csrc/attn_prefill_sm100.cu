@@ -7,10 +7,10 @@
 //
 //   warps 0-7    softmax, one warpgroup per Q tile, one thread per row (TMEM lane = row), so a
 //                row needs no exchange between threads.  The score tile is produced in steps
-//                of 64 keys into two alternating TMEM buffers: while the warpgroup works on
-//                step i, the scores of step i+1 are already being computed.  Per step:
-//                tcgen05.ld the 64 scores once into registers, row max, scale, mask, exp2,
-//                pack P to 16 bit and tcgen05.st it over the first 32 columns of the buffer.
+//                of 64 keys into the tile's one score buffer.  Per step: tcgen05.ld the 64
+//                scores into registers and hand the buffer back at once (the next step's scores
+//                are computed while this step's softmax runs), row max, scale, mask, exp2, pack
+//                P to 16 bit and tcgen05.st it into one of the tile's two probability buffers.
 //                The running max is only raised when it grows by more than 8 (log2 units),
 //                so the O accumulator in TMEM is rescaled rarely; the same warps write the
 //                normalised output
@@ -18,21 +18,28 @@
 //                two 2-stage rings; paged caches are fetched page by page with one
 //                4-D box per page and 64-column half, so a tile lands as a dense,
 //                128-byte-swizzled K-major tile
-//   warps 9,10   one tcgen05.mma issuing thread per Q tile: per step S = Q K^T as 8 SS MMAs
-//                (M128 N64 K16) and O += P V as 4 TS MMAs (M128 N128 K16, P read from TMEM as
-//                the A operand).  Order per tile: PV(i), then QK(i+2) into the buffer PV(i)
-//                has just released, so softmax(i+1) never waits for the tensor pipe's
-//                round trip.  Each tile has its own issuing thread so that one tile's MMAs do
-//                not queue behind the other's barrier waits
-// TMEM columns: tile t has score buffers at t*128 and t*128+64 and its output at 256+t*128;
-// P aliases the first 32 columns of its score buffer (keys [16k,16k+16) in columns 8k..8k+8).
+//   warps 9,10   one score-issuing thread per Q tile: S = Q K^T of a step as 8 SS MMAs (M128 N64
+//                K16), issued as soon as the softmax warps hold the previous step's scores in
+//                registers and the PV MMAs that read the probability buffer this step will fill
+//                (two steps back) have completed
+//   warp 11      one PV-issuing thread for both tiles: O += P V of a step as 4 TS MMAs per tile
+//                (M128 N128 K16, P read from TMEM as the A operand), tile 0 then tile 1, each as
+//                soon as its probabilities are stored.  Three issuing threads instead of one per
+//                tile: a thread that issues a step's 12 MMAs and 3-4 commits beside the softmax
+//                warps of its scheduler needs about as long as a softmax step, and with the score
+//                MMAs on threads of their own the tensor pipe's round trip is off the softmax
+//                warps' path (+2 % on the whole kernel; 12 warps still leave 170 registers a thread,
+//                a 13th would cap them at 128)
+// TMEM columns: tile t has its score buffer at t*128 (64 columns), its probability buffers at
+// t*128+64 and t*128+96 (32 packed columns each: keys [16k,16k+16) in columns 8k..8k+8) and its
+// output at 256+t*128.
 // Every wait in the kernel is an mbarrier wait with a time limit (no named barriers, no
 // register reallocation): a wait that gives up sets the device status word and the CTA drains.
 // The kernel is persistent: one CTA per SM keeps its shared memory, TMEM, tensor maps and barriers
 // and draws work items from a ticket counter (query blocks of a sequence from the longest causal
 // prefix to the shortest).  Nothing synchronises the CTA between items: the producer warp publishes
 // the next item through a two-slot ring and loads ahead, the roles follow the barrier phases with
-// running counters, and the first score steps of an item are computed while the previous output
+// running counters, and the first score step of an item is computed while the previous output
 // tile is still being normalised and stored.
 //
 // Measured costs that shaped this layout (B200, SM clocks, microbenchmarks on an otherwise
@@ -92,7 +99,7 @@ constexpr int STEP = 64;                      // keys per score step (one TMEM s
 constexpr int HALF_BYTES = 128 * 64 * 2;   // one [128 x 64] 128B-swizzled sub-tile
 constexpr int TILE_BYTES = 2 * HALF_BYTES; // 32 KB
 constexpr int TMA_WARP = 8, MMA_WARP0 = 9;
-constexpr int NUM_THREADS = 11 * 32;   // 8 softmax warps, TMA producer, two MMA issuers
+constexpr int NUM_THREADS = 12 * 32;   // 8 softmax warps, TMA producer, two score-MMA issuers, one PV-MMA issuer
 constexpr int SMEM_BYTES = 6 * TILE_BYTES + 1024 + 256;
 constexpr int TMEM_COLS = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
@@ -178,8 +185,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint64_t* k_empty = bars + 4;       // [2]
   uint64_t* v_full = bars + 6;        // [2]
   uint64_t* v_empty = bars + 8;       // [2]
-  uint64_t* s_full = bars + 10;       // [2 tiles][2 score buffers]
-  uint64_t* p_ready = bars + 14;      // [2 tiles][2 score buffers]
+  uint64_t* s_full = bars + 10;       // [2 tiles] scores of a step have landed in the tile's score buffer
+  uint64_t* s_free = bars + 12;       // [2 tiles] ... and have been read into registers: the next may overwrite them
+  uint64_t* p_ready = bars + 14;      // [2 tiles][2 probability buffers]
   uint64_t* o_done = bars + 18;       // [2 tiles][2]: PV of even / odd steps (a softmax warp can be two
                                       // steps ahead of the tensor pipe, one parity bit per barrier is not enough)
   uint64_t* o_free = bars + 22;       // [2 tiles] the output tile of the previous item has been read out
@@ -197,12 +205,13 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], NT);
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], NT);
+      mbar_init(&v_empty[i], 1);        // the one PV-issuing thread commits for both tiles
       mbar_init(&o_free[i], 4);       // one arrival per softmax warp of the tile
       mbar_init(&item_full[i], 1);
-      mbar_init(&item_empty[i], 5 * NT);   // per tile: the issuing thread and four softmax warps
+      mbar_init(&item_empty[i], 5 * NT + 1);   // per tile: the score-issuing thread and four softmax warps; the PV thread
     }
-    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&s_full[i], 1);
+    for (int i = 0; i < 2; ++i) mbar_init(&s_free[i], 4);    // one arrival per softmax warp of the tile
     for (int i = 0; i < 4; ++i) mbar_init(&p_ready[i], 4);   // one arrival per softmax warp of the tile
     for (int i = 0; i < 4; ++i) mbar_init(&o_done[i], 1);
     mbar_fence_init();
@@ -232,7 +241,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   // running counters (work items, K/V tiles, score steps), so nothing synchronises the CTA between
   // items: the producer warp draws the next item from the launch's ticket counter while the current
   // one is still being computed, publishes it through a two-slot ring and loads its Q and first K/V
-  // tiles as soon as the stages are free; the issuing threads compute its first two score steps
+  // tiles as soon as the stages are free; the score-issuing threads compute its first score step
   // while the softmax warps still normalise and store the previous output.
   struct Item {
     int m0, h0, b, n_steps, n_tiles, shift;
@@ -334,12 +343,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
         }
       }
     }
-  } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + NT) {
+  } else if (warp == MMA_WARP0 + 2 || (warp >= MMA_WARP0 && warp < MMA_WARP0 + NT)) {
     // ================================ MMA issuers =================================
+    // One thread per Q tile for the score MMAs and one thread for the PV MMAs of both tiles: a single
+    // thread per tile needs 1800-2000 clocks per step for both kinds beside the softmax warps of its
+    // scheduler (45-50 clocks per MMA and ~95 per commit when alone), as long as a softmax step.  The
+    // threads order their work through the barriers only (scores: S read out and the PV two steps
+    // back completed; PV: probabilities stored), never through issue order.
     // The descriptors are kept as 32-bit low words plus one constant high word so that an
-    // MMA costs one add per operand: the issuing thread shares its scheduler with four
-    // softmax warps and every instruction it spends is felt.
-    const int t = warp - MMA_WARP0;
+    // MMA costs one add per operand.
+    const bool pv_role = warp == MMA_WARP0 + 2;     // warps 9, 10: scores of tile 0, 1; warp 11: PV of both tiles
+    const int t = pv_role ? 0 : warp - MMA_WARP0;
     if (lane == 0) {
       constexpr bool bf16 = kBf16;
       const uint32_t idesc_qk = umma_idesc_f16(bf16, false, false, BM, STEP);  // A, B K-major, N = 64
@@ -363,58 +377,71 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #ifdef FG_PREFILL_TRACE
         const bool trace_on = blockIdx.x == 0 && g0 == 0;   // the first item this CTA computes
 #endif
-        // scores of step i of this item: keys [64 i, 64 i + 64) = rows (i & 1) * 64 .. of its K tile i >> 1;
-        // score buffer and barrier phases follow the running step count g0 + i
-        auto issue_qk = [&](int i) {
-          const uint32_t tile = kv0 + (uint32_t)(i >> 1), stg = tile & 1, g = g0 + (uint32_t)i;
-          if (!(i & 1) && !mbar_wait(&k_full[stg], (tile >> 1) & 1, abort_flag, a.status, FG_SITE(8))) {
-            ok = false;
-            return;
-          }
-          tc_fence_after();
-          const uint32_t k_lo = k_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (STEP * 128 >> 4);
+        if (!pv_role) {
+          // ---- scores of step i: keys [64 i, 64 i + 64) = rows (i & 1) * 64 .. of K tile i >> 1, into the
+          // tile's one score buffer as soon as the softmax warps hold the previous step's in registers
+          if (!mbar_wait(q_full, n_q & 1, abort_flag, a.status, FG_SITE(3))) break;
+          for (int i = 0; i < n_steps && ok; ++i) {
+            const uint32_t tile = kv0 + (uint32_t)(i >> 1), stg = tile & 1, g = g0 + (uint32_t)i;
+            if (!(i & 1) && !mbar_wait(&k_full[stg], (tile >> 1) & 1, abort_flag, a.status, FG_SITE(8))) {
+              ok = false;
+              break;
+            }
+            // the scores of the previous step (of this item or the one before) must have been read out
+            if (g > 0 && !mbar_wait(&s_free[t], (g - 1) & 1, abort_flag, a.status, FG_SITE(9))) {
+              ok = false;
+              break;
+            }
+            // The softmax warps will store P(i) over the buffer that the PV MMAs of step i - 2, issued by
+            // another thread, read: those must have completed before the scores of step i exist.  (Steps 0
+            // and 1 of an item follow the previous item's last PV, which the softmax warps wait for in
+            // their epilogue before they take the next item's first scores.)
+            if (i >= 2 && !mbar_wait(&o_done[t * 2 + (g & 1)], ((g - 2) >> 1) & 1, abort_flag, a.status, FG_SITE(18))) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t k_lo = k_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (STEP * 128 >> 4);
 #pragma unroll
-          for (int k = 0; k < HD / 16; ++k) {
-            const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
-            mma_f16_ss_lohi(s_tmem + (g & 1) * STEP, q_lo + off, k_lo + off, desc_hi, idesc_qk, k != 0 ? 1u : 0u);
+            for (int k = 0; k < HD / 16; ++k) {
+              const uint32_t off = ((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4;
+              mma_f16_ss_lohi(s_tmem, q_lo + off, k_lo + off, desc_hi, idesc_qk, k != 0 ? 1u : 0u);
+            }
+            tc_commit(&s_full[t]);
+            FG_TRACE(48 + t, i);
+            if ((i & 1) || i == n_steps - 1) tc_commit(&k_empty[stg]);   // last step on this K tile
+            if (i == n_steps - 1) tc_commit(q_empty);                    // last use of this item's Q
           }
-          tc_commit(&s_full[t * 2 + (g & 1)]);
-          FG_TRACE(48 + t, i);
-          if ((i & 1) || i == n_steps - 1) tc_commit(&k_empty[stg]);   // last step on this K tile
-          if (i == n_steps - 1) tc_commit(q_empty);                    // last use of this item's Q
-        };
-        if (!mbar_wait(q_full, n_q & 1, abort_flag, a.status, FG_SITE(3))) break;
-        issue_qk(0);
-        if (ok && n_steps > 1) issue_qk(1);
-        for (int i = 0; i < n_steps && ok; ++i) {
-          const uint32_t tile = kv0 + (uint32_t)(i >> 1), stg = tile & 1, g = g0 + (uint32_t)i;
-          if (!(i & 1) && !mbar_wait(&v_full[stg], (tile >> 1) & 1, abort_flag, a.status, FG_SITE(5))) {
-            ok = false;
-            break;
-          }
-          if (!mbar_wait(&p_ready[t * 2 + (g & 1)], (g >> 1) & 1, abort_flag, a.status, FG_SITE(6))) {
-            ok = false;
-            break;
-          }
-          // the first PV of an item overwrites the output tile: the previous one must have been read out
-          if (i == 0 && n_q > 0 && !mbar_wait(&o_free[t], (n_q - 1) & 1, abort_flag, a.status, FG_SITE(7))) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          FG_TRACE(0 + t, i);
-          const uint32_t v_lo = v_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (4 * 2048 >> 4);
-          const uint32_t p_tmem = s_tmem + (g & 1) * STEP;
+        } else {
+          // ---- O += P V of step i of both tiles, tile 0 first, once the probabilities are stored
+          for (int i = 0; i < n_steps && ok; ++i) {
+            const uint32_t tile = kv0 + (uint32_t)(i >> 1), stg = tile & 1, g = g0 + (uint32_t)i;
+            if (!(i & 1) && !mbar_wait(&v_full[stg], (tile >> 1) & 1, abort_flag, a.status, FG_SITE(5))) {
+              ok = false;
+              break;
+            }
+            const uint32_t v_lo = v_lo0 + stg * (TILE_BYTES >> 4) + (i & 1) * (4 * 2048 >> 4);
+            for (int tt = 0; tt < NT && ok; ++tt) {
+              if (!mbar_wait(&p_ready[tt * 2 + (g & 1)], (g >> 1) & 1, abort_flag, a.status, FG_SITE(6))) {
+                ok = false;
+                break;
+              }
+              // the first PV of an item overwrites the output tile: the previous one must have been read out
+              if (i == 0 && n_q > 0 && !mbar_wait(&o_free[tt], (n_q - 1) & 1, abort_flag, a.status, FG_SITE(7))) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              FG_TRACE(0 + tt, i);
+              const uint32_t p_tmem = tmem_base + tt * 128 + STEP + (g & 1) * 32;
+              const uint32_t o_tm = tmem_base + 256 + tt * 128;
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            mma_f16_ts_lohi(o_tmem, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
-          // The next scores are what the softmax warps wait for: they and their commit go first.  The
-          // commits below then also cover those score MMAs, i.e. "PV done" and "V stage free" are
-          // announced about 500 clocks later than they could be; the first is waited for only on a
-          // rescale and at the end of the item, the second has a whole K/V tile of slack.
-          if (i + 2 < n_steps) issue_qk(i + 2);
-          tc_commit(&o_done[t * 2 + (g & 1)]);
-          if ((i & 1) || i == n_steps - 1) tc_commit(&v_empty[stg]);     // last step on this V tile
+              for (int k = 0; k < 4; ++k)
+                mma_f16_ts_lohi(o_tm, p_tmem + k * 8, v_lo + k * (2048 >> 4), desc_hi, idesc_pv, (i > 0 || k > 0) ? 1u : 0u);
+              tc_commit(&o_done[tt * 2 + (g & 1)]);
+            }
+            if (ok && ((i & 1) || i == n_steps - 1)) tc_commit(&v_empty[stg]);     // last step on this V tile
+          }
         }
         ++n_q;
         kv0 += (uint32_t)it.n_tiles;
@@ -467,19 +494,24 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 
       for (int i = 0; i < n_steps; ++i) {
         const uint32_t g = g0 + (uint32_t)i;
-        const int sb = (int)(g & 1);                       // score buffer of this step
-        const uint32_t sb_addr = s_addr + sb * STEP;
+        const int sb = (int)(g & 1);                       // probability buffer of this step
+        const uint32_t p_addr = s_addr + STEP + sb * 32;
+
         if (quarter == 0) FG_TRACE(8 + t * 16, i);
-        if (!wwait(&s_full[t * 2 + sb], (g >> 1) & 1, 10)) {
+        if (!wwait(&s_full[t], g & 1, 10)) {
           ok = false;
           break;
         }
         tc_fence_after();
         if (quarter == 0) FG_TRACE(4 + t * 16, i);
         float sv[64];
-        tmem_ld32(sb_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-        tmem_ld32(sb_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        tmem_ld32(s_addr, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        tmem_ld32(s_addr + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
         tmem_ld_wait();
+        // the scores are in registers: the next step's may be computed into the same columns
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&s_free[t]);
         const int col0 = i * STEP;
         if ((col0 + STEP > s.k_len) || (a.causal && (col0 + STEP - 1 > m0 + shift))) {
           int lim = s.k_len - 1;                         // last visible column of this row
@@ -558,8 +590,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
 #pragma unroll
           for (int e = 0; e < 64; e += 2) fma2(sv[e], sv[e + 1], sc2, ng2);
         }
+        if (quarter == 0) FG_TRACE(10 + t * 16, i);
 #pragma unroll
         for (int e = 0; e < 64; ++e) sv[e] = ex2(sv[e]);
+        if (quarter == 0) FG_TRACE(11 + t * 16, i);
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           uint32_t pk[16];
@@ -569,10 +603,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
             add2(sum4[(e & 1) * 2], sum4[(e & 1) * 2 + 1], p0, p1);
             pk[e] = bf16 ? pack_bf16(p0, p1) : pack_f16(p0, p1);
           }
-          tmem_st16(sb_addr + q * 16, pk);
+          tmem_st16(p_addr + q * 16, pk);
         }
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (quarter == 0) FG_TRACE(12 + t * 16, i);
         tmem_st_wait();
+        if (quarter == 0) FG_TRACE(13 + t * 16, i);
         tc_fence_before();
         __syncwarp();
         if (quarter == 0) FG_TRACE(56 + t, i);
