@@ -364,7 +364,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       const uint32_t q_lo = (uint32_t)umma_desc_sw128(smem_u32(sQ + t * TILE_BYTES), 0, 1024);
       const uint32_t k_lo0 = (uint32_t)umma_desc_sw128(smem_u32(sK), 0, 1024);
       const uint32_t v_lo0 = (uint32_t)umma_desc_sw128(smem_u32(sV), HALF_BYTES, 1024);
-      const uint32_t s_tmem = tmem_base + t * 128, o_tmem = tmem_base + 256 + t * 128;
+      const uint32_t s_tmem = tmem_base + t * 128;   // the score thread's tile
       uint32_t n_it = 0, n_q = 0, kv0 = 0, g0 = 0;   // items read, items computed, K/V tiles and score steps before this item
       bool ok = true;
       while (ok) {
