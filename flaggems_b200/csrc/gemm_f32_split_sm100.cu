@@ -2,7 +2,8 @@
 // fp32 A, B, bias and C, with an error at the level of fp32 arithmetic on CUDA cores.
 //
 // Each operand is first written as three bf16 pieces, x = hi + mid + lo exactly (8 + 8 + 8
-// mantissa bits), by `split3_kernel`.  The product is then the sum of six piece products in
+// mantissa bits; values below about 2^-100, whose third piece is a bf16 denormal, lose less than
+// 2^-133), by `split3_kernel`.  The product is then the sum of six piece products in
 // ascending order of magnitude,
 //     mid*mid, hi*lo, lo*hi      (2^-16 of the result)
 //     hi*mid, mid*hi             (2^-8)
@@ -353,7 +354,7 @@ __global__ void __launch_bounds__(256) split3_kernel(const float* __restrict__ x
       if (isinf(fh)) fh = __uint_as_float(__float_as_uint(xv) & 0xffff0000u);
       const float r1 = xv - fh;                                   // exact
       const float fm = __bfloat162float(__float2bfloat16_rn(r1));
-      const float r2 = r1 - fm;                                   // exact, fits 8 bits
+      const float r2 = r1 - fm;                                   // exact; fits 8 bits unless denormal as bf16
       h[j] = fh; m[j] = fm; l[j] = r2;
     }
     __nv_bfloat16* dst = planes + r * ld_out + c0;

@@ -132,6 +132,55 @@ def test_f32_split_workspace_is_pure_host_logic():
     assert _lib.load().fg_gemm_f32_split(ctypes.byref(p), None, 0, None) == -2    # FG_ERR_UNSUPPORTED, nothing launched
 
 
+def test_three_bf16_pieces_carry_an_fp32_value_exactly():
+    """The arithmetic of the fp32 tensor-core GEMM's split pass (csrc/gemm_f32_split_sm100.cu, split3_kernel),
+    restated with numpy: hi = bf16(x) rounded to nearest even (truncated when rounding would overflow to
+    infinity), mid = bf16(x - hi), lo = x - hi - mid.  The three pieces must add up to x exactly and be bf16
+    values (the third one outside the denormal range), and the three piece products the kernel drops must stay below 2^-22 of |a b|."""
+    import numpy as np
+
+    def bf16_rn(x):                                   # float32 -> nearest-even bfloat16, kept as float32
+        u = x.astype(np.float32).view(np.uint32).astype(np.uint64)
+        r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32)
+        return r.view(np.float32)
+
+    def split3(x):
+        with np.errstate(over="ignore", invalid="ignore"):
+            hi = bf16_rn(x)
+            trunc = (x.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+            hi = np.where(np.isinf(hi), trunc, hi)
+            r1 = x - hi
+            mid = bf16_rn(r1)
+            lo = r1 - mid
+        return hi, mid, lo
+
+    rng = np.random.default_rng(0)
+    x = np.concatenate([
+        rng.standard_normal(200000).astype(np.float32),
+        (rng.standard_normal(50000) * 1e30).astype(np.float32),
+        (rng.standard_normal(50000) * 1e-30).astype(np.float32),
+        np.array([3.4e38, -3.4e38, 3.3895314e38, 1.0, -1.0, 0.0, 1.0 + 2.0 ** -23, 255.99998, 2.0 ** -100], np.float32),
+        rng.integers(0x00800000, 0x7F7FFFFF, 200000, dtype=np.uint32).view(np.float32),     # every exponent and mantissa
+    ])
+    hi, mid, lo = split3(x)
+    for piece in (hi, mid, lo):
+        assert np.all(np.isfinite(piece))
+    assert np.array_equal(hi.astype(np.float64) + mid.astype(np.float64) + lo.astype(np.float64), x.astype(np.float64))
+    is_bf16 = lambda v: (v.view(np.uint32) & 0xFFFF) == 0
+    assert np.all(is_bf16(hi)) and np.all(is_bf16(mid))
+    # the third piece is a bfloat16 value too unless it falls into the denormal range (|x| below 2^-100 or so);
+    # there the kernel's final rounding of it costs less than the denormal spacing 2^-133
+    big = np.abs(x) >= 2.0 ** -100
+    assert np.all(is_bf16(lo[big]))
+    assert np.max(np.abs(bf16_rn(lo).astype(np.float64) - lo.astype(np.float64))) <= 2.0 ** -134
+    # the kernel multiplies hi*hi, hi*mid, mid*hi, hi*lo, lo*hi, mid*mid; what it leaves out:
+    a, b = x[:200000].astype(np.float64), x[200000 - 1::-1][:200000].astype(np.float64)
+    ah, am, al = (v[:200000].astype(np.float64) for v in (hi, mid, lo))
+    bh, bm, bl = (v[200000 - 1::-1][:200000].astype(np.float64) for v in (hi, mid, lo))
+    kept = ah * bh + ah * bm + am * bh + ah * bl + al * bh + am * bm
+    assert np.max(np.abs(a * b - kept) / np.abs(a * b)) < 2.0 ** -22
+
+
 def test_attention_path_selection():
     def params(max_q, batch, total_q, hq=32, hk=8, d=128, alibi=False, wl=-1):
         p = _lib.AttnParams()
