@@ -528,8 +528,9 @@ def extra_op_times(device, peaks, reps=10, full=False):
     """Operator forms that are not part of `value`, each timed on its own (L2 emptied before every call):
     reshape_and_cache_flash on all K/V rows of the prefill batch (the size at which a GB/s figure
     means something), rotary_embedding out of place, and the four projections with a column-major
-    B.  With `full` also the operators of the next scope rows: aten::_flash_attention_forward on a
-    dense causal GQA batch (packed and as the transposed views SDPA passes), bmm, gelu_and_mul."""
+    B, and a 4096^3 fp32 mm (the tensor-core form from bf16 pieces).  With `full` also the operators of the
+    next scope rows: aten::_flash_attention_forward on a dense causal GQA batch (packed and as the
+    transposed views SDPA passes), bmm, gelu_and_mul."""
     import flaggems_b200 as fg
     from flaggems_b200 import workloads as W
 
@@ -573,6 +574,15 @@ def extra_op_times(device, peaks, reps=10, full=False):
             ms = timed_median(lambda: fg.mm_out(a, b, out=c), flush, reps)
             entry(f"mm[{name}] with column-major B", ms, 2 * M * N * K, "tensor")
         del a, b, c
+    # fp32 mm (never TF32): at this size three bf16 pieces per operand on the tensor cores, chunked accumulation
+    g32 = torch.Generator(device=device).manual_seed(78)
+    a32 = torch.randn((4096, 4096), generator=g32, dtype=torch.float32, device=device)
+    b32 = torch.randn((4096, 4096), generator=g32, dtype=torch.float32, device=device)
+    ms = timed_median(lambda: fg.mm(a32, b32), flush, max(3, reps // 3), warm=1)
+    out.append({"op": "mm fp32 4096 x 4096 x 4096 (no TF32; incl. output and scratch allocation)", "ms": round(ms, 4),
+                "bound": "tensor (six bf16 piece products per fp32 product)", "achieved": round(2 * 4096 ** 3 / ms / 1e9, 1),
+                "unit": "TFLOP/s"})
+    del a32, b32
     if not full:
         return out
     g = torch.Generator(device="cpu").manual_seed(77)
@@ -598,13 +608,6 @@ def extra_op_times(device, peaks, reps=10, full=False):
         with torch.no_grad():
             ms = timed_median(lambda: fg.gelu_and_mul(x[:, :half], x[:, half:], approximate), flush, reps)
         entry(f"gelu_and_mul[{approximate}] halves of [4096, 22016] (incl. output allocation)", ms, nbytes, "hbm")
-    # fp32 mm (never TF32): at this size three bf16 pieces per operand on the tensor cores, chunked accumulation
-    a32 = torch.randn((4096, 4096), generator=g, dtype=torch.float32).to(device)
-    b32 = torch.randn((4096, 4096), generator=g, dtype=torch.float32).to(device)
-    ms = timed_median(lambda: fg.mm(a32, b32), flush, max(3, reps // 3), warm=1)
-    out.append({"op": "mm fp32 4096 x 4096 x 4096 (no TF32; incl. output allocation)", "ms": round(ms, 4),
-                "bound": "tensor (six bf16 piece products per fp32 product)", "achieved": round(2 * 4096 ** 3 / ms / 1e9, 1),
-                "unit": "TFLOP/s"})
     return out
 
 
@@ -1009,7 +1012,7 @@ def main():
     ap.add_argument("--only", default="", help="run (and allocate) only the operators whose name contains this string")
     ap.add_argument("--extra", action="store_true",
                     help="N=1: extra_ops also covers the operators built beyond the benchmark step (dense "
-                         "_flash_attention_forward, gelu_and_mul, bmm, fp32 mm)")
+                         "_flash_attention_forward, gelu_and_mul, bmm)")
     ap.add_argument("--no-extra", action="store_true", help="N=1: skip extra_ops altogether")
     ap.add_argument("--no-triton-ref", action="store_true",
                     help="N=1: do not time the unmodified reference's Triton kernels (baseline/_ref) beside ours; "
